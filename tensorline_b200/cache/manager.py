@@ -35,16 +35,18 @@ from .pages import CacheError, PagePool, page_hash
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values of `num_kv_heads` heads of `head_dim`, all of them (`window` None) or
-    the last `window` positions.  `shared_values`: the value of a token is its key row itself (a mixer that
-    caches one latent vector a token): one page tensor serves as both."""
+    the last `window` positions and, with `keep_first`, the first `keep_first` positions of the request as well (they
+    stay readable however far the window has moved).  `shared_values`: the value of a token is its key row itself (a
+    mixer that caches one latent vector a token): one page tensor serves as both."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     shared_values: bool = False
+    keep_first: int = 0
 
     @property
     def group_key(self):
-        return ("paged_kv", self.window)
+        return ("paged_kv", self.window, self.keep_first if self.window is not None else 0)
 
 
 @dataclass(frozen=True)
@@ -63,6 +65,7 @@ class PageGroup:
     index: int
     window: int | None
     pool: PagePool
+    keep_first: int = 0                                 # a window group never gives back the pages of these positions
     caches: list = field(default_factory=list)          # ids of the cache entries that use this group
     table: np.ndarray | None = None                     # [max_slots + 1, max_pages_per_seq] int32
     version: int = 0                                    # bumped at every write to `table`
@@ -107,7 +110,10 @@ class CacheManager:
             g = by_key.get(need.group_key)
             if g is None:
                 n = num_pages[need.window] if isinstance(num_pages, dict) else num_pages
-                g = PageGroup(len(self.groups), need.window, PagePool(n, False))
+                if need.keep_first < 0:
+                    raise ValueError(f"cache {cid!r}: keep_first must not be negative")
+                g = PageGroup(len(self.groups), need.window, PagePool(n, False),
+                              keep_first=need.keep_first if need.window is not None else 0)
                 g.table = np.full((max_num_seqs + 1, self.max_pages_per_seq), n, dtype=np.int32)
                 by_key[need.group_key] = g
                 self.groups.append(g)
@@ -145,7 +151,8 @@ class CacheManager:
     def can_ever_hold(self, num_tokens: int) -> bool:
         """Whether a request of `num_tokens` tokens could lie in an otherwise empty cache."""
         for g in self.groups:
-            live = num_tokens if g.window is None else min(num_tokens, g.window + self.page_size)
+            live = num_tokens if g.window is None else \
+                min(num_tokens, g.window + self.page_size + self._kept_pages(g) * self.page_size)
             if -(-live // self.page_size) > g.pool.num_pages:
                 return False
         return True
@@ -176,7 +183,7 @@ class CacheManager:
         for g, pages in zip(self.groups, held.pages):
             first = self._first_needed_page(g, start)
             # a passed page that others share comes back to nobody: count the request's own only
-            returning = sum(1 for p in pages[:first] if p >= 0 and g.pool.refcount(p) == 1)
+            returning = sum(1 for p in pages[self._kept_pages(g):first] if p >= 0 and g.pool.refcount(p) == 1)
             room = min(room, (len(pages) + g.pool.num_free + returning) * self.page_size - start)
         return max(0, room)
 
@@ -208,7 +215,7 @@ class CacheManager:
                 most = k
         for k in range(most, 0, -1):
             if all(served(g, i) for g in self.groups if g.window is not None
-                   for i in range(self._first_needed_page(g, k * ps), k)):
+                   for i in self._needed_pages(g, k * ps, k)):
                 return k, digests[:k]
         return 0, []
 
@@ -230,22 +237,33 @@ class CacheManager:
             return 0
         held.digests = digests
         for g, pages in zip(self.groups, held.pages):
-            first = self._first_needed_page(g, k * ps)
-            pages += [-1] * first                        # what the window has passed is never read
-            for i in range(first, k):
+            pages += [-1] * k                            # what the window has passed is never read
+            for i in self._needed_pages(g, k * ps, k):
                 page = g.pool.adopt(digests[i], digests[i - 1] if i else None, tokens[i * ps:(i + 1) * ps])
                 if page is None:
                     raise CacheError(f"published page {i} of group {g.index} vanished during admission")
-                pages.append(page)
+                pages[i] = page
             held.offered[g.index] = k
-            self._write_table(g.index, held.slot, first, pages[first:])
+            for i, page in enumerate(pages):
+                if page >= 0:
+                    self._write_table(g.index, held.slot, i, [page])
         return k * ps
 
     def _first_needed_page(self, g: PageGroup, start: int) -> int:
-        """Index of the first page a query at position >= `start` can still read."""
+        """Index of the first page a query at position >= `start` can still read through its window."""
         if g.window is None:
             return 0
         return max(0, start - g.window + 1) // self.page_size
+
+    def _kept_pages(self, g: PageGroup) -> int:
+        """Leading pages of a window group that hold a position every later query reads (`keep_first`): never given back."""
+        return -(-g.keep_first // self.page_size) if g.window is not None else 0
+
+    def _needed_pages(self, g: PageGroup, start: int, upto: int) -> list:
+        """Indices below `upto` of the pages a query at position >= `start` can read: all of them, or the kept ones and
+        those the window reaches."""
+        first = max(self._first_needed_page(g, start), self._kept_pages(g))
+        return list(range(min(self._kept_pages(g), upto))) + list(range(min(first, upto), upto))
 
     def grow(self, rid, start: int, upto: int) -> bool:
         """Make room for positions [start, upto): first give back what every window has passed
@@ -273,7 +291,7 @@ class CacheManager:
             if g.window is None:
                 continue
             first = min(self._first_needed_page(g, start), len(pages))
-            gone = [(i, p) for i, p in enumerate(pages[:first]) if p >= 0]
+            gone = [(i, p) for i, p in enumerate(pages[:first]) if p >= 0 and i >= self._kept_pages(g)]
             if gone:
                 g.pool.drop([p for _, p in gone])
                 self._touch(g)

@@ -7,6 +7,8 @@
 // s = (q . k) * scale, softmax over keys in float, o = P V (tensorline/paged_attn.py:46-57).
 // `sink` (float per query head, may be null): the denominator also holds exp(sink[h]), a term with no
 // key and no value that is not scaled and counts once.
+// `keep_first` (with a window): the keys at positions below it are read as well, however far the window has moved.
+// `gate` (float [T, nq], may be null): the finished row is multiplied by sigmoid(gate[t, h]).
 //
 // Keys are taken in tiles of 32 aligned to absolute position 0, each lane owning one key of the
 // tile, with a running maximum and sum.  The order of every addition depends only on the
@@ -22,7 +24,8 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
                                       const int* __restrict__ table, int max_pages, int page_size,
                                       const int* __restrict__ pos, const int* __restrict__ req_slot,
                                       int nq, int nkv, int d, int window, float scale,
-                                      const float* __restrict__ sink, const TlLimits L) {
+                                      const float* __restrict__ sink, int keep_first, const float* __restrict__ gate,
+                                      const TlLimits L) {
     __shared__ float qs[ATT_MAX_D];
     const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int kh = h / (nq / nkv);
@@ -39,9 +42,12 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
     for (int c = 0; c < MAXC; ++c) acc[c] = 0.f;
     float m = -INFINITY, l = 0.f;
 
-    for (int j0 = (lo / 32) * 32; j0 <= p; j0 += 32) {
+    // tiles of 32 keys from position 0 on; those that lie wholly between the kept first keys and the window are skipped
+    const int kept = min(keep_first, lo);                // keys [0, kept) and [lo, p]
+    for (int j0 = 0; j0 <= p; j0 += 32) {
+        if (j0 >= kept && j0 + 32 <= lo) { j0 = (lo / 32) * 32 - 32; continue; }
         const int j = j0 + lane;
-        const bool valid = (j >= lo) && (j <= p);
+        const bool valid = (j >= lo || j < kept) && (j <= p);
         size_t row = 0;
         float s = -INFINITY;
         if (valid) {
@@ -81,7 +87,8 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
         for (int c = 0; c < MAXC; ++c) acc[c] *= alpha;
     }
     TA* orow = out + ((size_t)t * nq + h) * d;
-    const float inv = 1.0f / l;
+    float inv = 1.0f / l;
+    if (gate) inv *= 1.0f / (1.0f + expf(-gate[(size_t)t * nq + h]));
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
         const int e = lane + 32 * c;
@@ -92,8 +99,8 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
 TL_EXPORT int tl_attn_tokenwise(const void* q, int q_stride, void* out, int act_dtype,
                                 const void* k_pages, const void* v_pages, const int* table, int max_pages,
                                 int page_size, const int* pos, const int* req_slot, int T, int nq, int nkv,
-                                int d, int window, float scale, const float* sink, int table_rows, int total_pages,
-                                int* fault, cudaStream_t stream) {
+                                int d, int window, float scale, const float* sink, int keep_first, const float* gate,
+                                int table_rows, int total_pages, int* fault, cudaStream_t stream) {
     const TlLimits L{table_rows, total_pages, fault};
     if (T <= 0) return 0;
     if (d > ATT_MAX_D || nq % nkv) return 1;
@@ -101,10 +108,10 @@ TL_EXPORT int tl_attn_tokenwise(const void* q, int q_stride, void* out, int act_
     if (act_dtype == TL_F32)
         attn_tokenwise_kernel<float><<<grid, 32, 0, stream>>>((const float*)q, q_stride, (float*)out,
             (const float*)k_pages, (const float*)v_pages, table, max_pages, page_size, pos, req_slot,
-            nq, nkv, d, window, scale, sink, L);
+            nq, nkv, d, window, scale, sink, window > 0 ? keep_first : 0, gate, L);
     else
         attn_tokenwise_kernel<bf16><<<grid, 32, 0, stream>>>((const bf16*)q, q_stride, (bf16*)out,
             (const bf16*)k_pages, (const bf16*)v_pages, table, max_pages, page_size, pos, req_slot,
-            nq, nkv, d, window, scale, sink, L);
+            nq, nkv, d, window, scale, sink, window > 0 ? keep_first : 0, gate, L);
     return tl_launch_status();
 }

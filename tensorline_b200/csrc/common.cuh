@@ -185,9 +185,25 @@ __device__ __forceinline__ float tl_act(float g, int act) {
     return g / (1.0f + expf(-g));
 }
 
+// The clamped swish works on the pair: g' = min(g, limit), u' = clamp(u, -limit, limit); g' sigmoid(alpha g') (u' + 1).
+#define TL_ACT_SWISH_CLAMPED 3
+__device__ __forceinline__ float tl_swish_clamped(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+// act(g) * u for every code above, exact arithmetic; `limit` and `alpha` are the clamped swish's constants
+__device__ __forceinline__ float tl_act_pair(float g, float u, int act, float limit, float alpha) {
+    return act == TL_ACT_SWISH_CLAMPED ? tl_swish_clamped(g, u, limit, alpha) : tl_act(g, act) * u;
+}
+
 // The gate of a gated product's epilogue: `kind` 1: silu(g) * u as every bfloat16 path computes it, 2: the tanh form of gelu.
 __device__ __forceinline__ float tl_gate_mul(float g, float u, int kind) {
     return kind == 2 ? tl_gelu_tanh(g) * u : tl_silu_mul(g, u);
+}
+// The same with `kind` 3: the clamped swish with its two constants.
+__device__ __forceinline__ float tl_gate_mul(float g, float u, int kind, float limit, float alpha) {
+    return kind == 3 ? tl_swish_clamped(g, u, limit, alpha) : tl_gate_mul(g, u, kind);
 }
 
 // Programmatic dependent launch.  A kernel launched with launch_after_wait() may be placed on the SMs while

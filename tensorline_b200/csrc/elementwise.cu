@@ -15,22 +15,22 @@ TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 // ------------------------------------------------------------------ embedding
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ x, const TW* __restrict__ table,
-                             const int* __restrict__ ids, int H) {
+                             const int* __restrict__ ids, int H, float scale) {
     const int t = blockIdx.x;
     grid_dependency_wait();
     grid_dependency_trigger();
     const TW* row = table + (size_t)ids[t] * H;
     float* out = x + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_f<TW>(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_f<TW>(row[i]) * scale;      // * 1.0f is exact
 }
 
-TL_EXPORT int tl_embed(void* x, const void* table, int table_dtype, const int* ids, int T, int H,
+TL_EXPORT int tl_embed(void* x, const void* table, int table_dtype, const int* ids, int T, int H, float scale,
                        cudaStream_t stream) {
     if (T <= 0) return 0;
     if (table_dtype == TL_F32)
-        launch_after_wait(embed_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)x, (const float*)table, ids, H);
+        launch_after_wait(embed_kernel<float>, dim3(T), dim3(256), 0, stream, (float*)x, (const float*)table, ids, H, scale);
     else
-        launch_after_wait(embed_kernel<bf16>, dim3(T), dim3(256), 0, stream, (float*)x, (const bf16*)table, ids, H);
+        launch_after_wait(embed_kernel<bf16>, dim3(T), dim3(256), 0, stream, (float*)x, (const bf16*)table, ids, H, scale);
     return tl_launch_status();
 }
 
@@ -218,7 +218,8 @@ TL_EXPORT int tl_add_rmsnorm(void* x, const void* r, const void* w, int w_dtype,
 // (gate in [0, I), up in [I, 2I)); blk = 64 is what a product against interleaved weight rows leaves.
 // `act` picks the gate's function: TL_ACT_SILU, or TL_ACT_GELU_TANH (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).
 template <typename TA>
-__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, int blk, size_t total, int act) {
+__global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int I, int blk, size_t total, int act,
+                                float limit, float alpha) {
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / I;
@@ -227,6 +228,7 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
         const float g = to_f<TA>(gu[t * 2 * I + gc]);
         const float u = to_f<TA>(gu[t * 2 * I + gc + blk]);
         if (act == TL_ACT_GELU_TANH) out[idx] = from_f<TA>(tl_gelu_tanh(g) * u);
+        else if (act == TL_ACT_SWISH_CLAMPED) out[idx] = from_f<TA>(tl_swish_clamped(g, u, limit, alpha));
         else if constexpr (sizeof(TA) == 4) out[idx] = (g / (1.0f + expf(-g))) * u;     // the 32-bit engine: exact division
         else                           out[idx] = from_f<TA>(tl_silu_mul(g, u));
     }
@@ -236,7 +238,8 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
 // groups, tokens): no division per element; with many tokens a thread takes two chunks a block's width apart,
 // so four 16-byte loads are in flight before the first is used; with few it takes one, for more blocks.
 template <int CHUNKS, int ACT>
-__global__ void __launch_bounds__(256) silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, int blk) {
+__global__ void __launch_bounds__(256) silu_mul_vec8_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, int I, int blk,
+                                                            float limit, float alpha) {
     const size_t t = blockIdx.y;
     const int c0 = (blockIdx.x * 256 * CHUNKS + threadIdx.x) * 8;
     grid_dependency_wait();
@@ -266,20 +269,24 @@ __global__ void __launch_bounds__(256) silu_mul_vec8_kernel(const bf16* __restri
             const float g0 = __low2float(g2[e]), g1 = __high2float(g2[e]);
             const float u0 = __low2float(u2[e]), u1 = __high2float(u2[e]);
             if (ACT == TL_ACT_GELU_TANH) o2[e] = __floats2bfloat162_rn(tl_gelu_tanh(g0) * u0, tl_gelu_tanh(g1) * u1);
+            else if (ACT == TL_ACT_SWISH_CLAMPED)
+                o2[e] = __floats2bfloat162_rn(tl_swish_clamped(g0, u0, limit, alpha), tl_swish_clamped(g1, u1, limit, alpha));
             else o2[e] = __floats2bfloat162_rn(tl_silu_mul(g0, u0), tl_silu_mul(g1, u1));
         }
         *reinterpret_cast<uint4*>(out + t * I + cs[k]) = ov;
     }
 }
 
-TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I, int blk, int act, cudaStream_t stream) {
+TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I, int blk, int act, float limit, float alpha,
+                          cudaStream_t stream) {
     const size_t total = (size_t)T * I;
     if (total == 0) return 0;
-    if (blk <= 0 || I % blk || (act != TL_ACT_SILU && act != TL_ACT_GELU_TANH)) return 1;
+    if (blk <= 0 || I % blk || (act != TL_ACT_SILU && act != TL_ACT_GELU_TANH && act != TL_ACT_SWISH_CLAMPED)) return 1;
     const int threads = 256;
     if (act_dtype == TL_BF16 && (I & 7) == 0 && (blk & 7) == 0 && T <= 65535 && ((((uintptr_t)gu | (uintptr_t)out) & 15) == 0)) {
 #define SMV(CH, A) launch_after_wait(silu_mul_vec8_kernel<CH, A>, dim3((unsigned)((I / 8 + 256 * CH - 1) / (256 * CH)), (unsigned)T), dim3(threads), 0, stream, \
-                                 (const bf16*)gu, (bf16*)out, I, blk)
+                                 (const bf16*)gu, (bf16*)out, I, blk, limit, alpha)
+        if (act == TL_ACT_SWISH_CLAMPED) return T >= 256 ? SMV(2, TL_ACT_SWISH_CLAMPED) : SMV(1, TL_ACT_SWISH_CLAMPED);
         if (act == TL_ACT_GELU_TANH) return T >= 256 ? SMV(2, TL_ACT_GELU_TANH) : SMV(1, TL_ACT_GELU_TANH);
         return T >= 256 ? SMV(2, TL_ACT_SILU) : SMV(1, TL_ACT_SILU);
 #undef SMV
@@ -287,9 +294,9 @@ TL_EXPORT int tl_silu_mul(const void* gu, void* out, int act_dtype, int T, int I
     const size_t cap = (size_t)tl_num_sms() * 16;
     const int blocks = (int)((total + threads - 1) / threads < cap ? (total + threads - 1) / threads : cap);
     if (act_dtype == TL_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, blk, total, act);
+        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, blk, total, act, limit, alpha);
     else
-        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, blk, total, act);
+        silu_mul_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, blk, total, act, limit, alpha);
     return tl_launch_status();
 }
 
@@ -460,4 +467,74 @@ TL_EXPORT int tl_post_norm_add_norm(void* x, const void* a, const void* w_post, 
                               : launch_post_norm<bf16, bf16>(x, a, w_post, extra, w_pre, out, rows, R, H, eps, write_x, stream);
     }
     return e ? e : tl_launch_status();
+}
+
+
+// ------------------------------------------------------------------ the residual sum and two norms of one stream
+// For blocks whose two sub-blocks read the same stream (x += mixer(norm1(x)) + feed_forward(norm2(x))):
+//   x += a + b   (either may be null; the two are added first, then to x);   h1 = x / rms(x) * w1;   h2 = x / rms(x) * w2
+// all in float, one block a row, one set of statistics for both norms; only h1 and h2 are rounded.  `h2` null: one norm.
+// `rows`: only those rows are produced and x is left alone.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256) add_rmsnorm_pair_kernel(float* __restrict__ x, const TA* __restrict__ a, const TA* __restrict__ b,
+                                                               const TW* __restrict__ w1, const TW* __restrict__ w2, TA* __restrict__ h1,
+                                                               TA* __restrict__ h2, const int* __restrict__ rows, int H, float eps) {
+    __shared__ float red[33];
+    const int i = blockIdx.x;
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const size_t src = (size_t)(rows ? rows[i] : i) * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = x[src + c];
+        if (a) {
+            const float add = b ? to_f<TA>(a[src + c]) + to_f<TA>(b[src + c]) : to_f<TA>(a[src + c]);
+            v += add;
+            if (!rows) x[src + c] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = x[src + c];                            // its own write of the first pass, or the untouched row
+        if (a && rows) v += b ? to_f<TA>(a[src + c]) + to_f<TA>(b[src + c]) : to_f<TA>(a[src + c]);
+        const float n = v * rstd;
+        h1[(size_t)i * H + c] = from_f<TA>(n * to_f<TW>(w1[c]));
+        if (h2) h2[(size_t)i * H + c] = from_f<TA>(n * to_f<TW>(w2[c]));
+    }
+}
+
+TL_EXPORT int tl_add_rmsnorm_pair(float* x, const void* a, const void* b, const void* w1, const void* w2, int w_dtype, void* h1,
+                                  void* h2, int act_dtype, const int* rows, int R, int H, float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (b && !a) return 1;
+#define ARP(TA, TW) launch_after_wait(add_rmsnorm_pair_kernel<TA, TW>, dim3(R), dim3(256), 0, stream, x, (const TA*)a, (const TA*)b, \
+        (const TW*)w1, (const TW*)w2, (TA*)h1, (TA*)h2, rows, H, eps)
+    if (act_dtype == TL_F32) { if (w_dtype == TL_F32) ARP(float, float); else ARP(float, bf16); }
+    else { if (w_dtype == TL_F32) ARP(bf16, float); else ARP(bf16, bf16); }
+#undef ARP
+    return tl_launch_status();
+}
+
+// ------------------------------------------------------------------ a sigmoid gate per (token, head) on attention's output
+// o[t, h, :] *= sigmoid(gate[t, h]); gate float [T, nq].
+template <typename TA>
+__global__ void head_gate_kernel(TA* __restrict__ o, const float* __restrict__ gate, int d, size_t total) {
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const float g = 1.0f / (1.0f + expf(-gate[idx / d]));
+        o[idx] = from_f<TA>(to_f<TA>(o[idx]) * g);
+    }
+}
+
+TL_EXPORT int tl_head_gate(void* o, int act_dtype, const float* gate, int T, int nq, int d, cudaStream_t stream) {
+    const size_t total = (size_t)T * nq * d;
+    if (total == 0) return 0;
+    const size_t cap = (size_t)tl_num_sms() * 16;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < cap ? (total + 255) / 256 : cap);
+    if (act_dtype == TL_F32) launch_after_wait(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)o, gate, d, total);
+    else launch_after_wait(head_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)o, gate, d, total);
+    return tl_launch_status();
 }

@@ -158,6 +158,98 @@ TL_EXPORT int tl_topk_softmax(const float* z, int ldz, int E, int top, int* idx,
     return tl_launch_status();
 }
 
+// ------------------------------------------------------------------ choice of experts among groups
+// One warp per token.  s = sigmoid(z); the choice scores are c = s + correction.  The experts form `groups` equal groups
+// of neighbours; a group's score is the sum of its `gtop` largest c; the `keep` groups with the largest scores stay, the
+// experts of the others cannot be chosen (their c may be anything, also negative).  `top` rounds of a warp-wide arg-max
+// over c among the experts that stay (largest value, lowest index on a tie); the weights are the chosen experts' s divided
+// by their sum (+ 1e-20), times `scale`.  E <= 1024, top <= 32.  Shared memory: c [E], s [E], the groups' scores [groups].
+__global__ void __launch_bounds__(32) route_groups_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction,
+                                                          int E, int top, int groups, int keep, int gtop, float scale,
+                                                          int* __restrict__ idx, float* __restrict__ wts) {
+    extern __shared__ float sm[];
+    float* c = sm;
+    float* s = sm + E;
+    float* gs = sm + 2 * E;
+    const int t = blockIdx.x, lane = threadIdx.x;
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const float* row = z + (size_t)t * ldz;
+    for (int e = lane; e < E; e += 32) {
+        const float sv = 1.0f / (1.0f + expf(-row[e]));
+        s[e] = sv;
+        c[e] = sv + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    const int per = E / groups;
+    // a group's score: the sum of its gtop largest choice scores (all of them, if it has fewer), taken largest first
+    for (int g = lane; g < groups; g += 32) {
+        const float* cg = c + g * per;
+        float sum = 0.f, last = INFINITY; int last_i = -1;
+        for (int r = 0; r < gtop && r < per; ++r) {
+            float best = -INFINITY; int bi = -1;
+            for (int i = 0; i < per; ++i) {
+                const float v = cg[i];
+                const bool below = v < last || (v == last && i > last_i);      // not one of those already taken
+                if (below && (bi < 0 || v > best)) { best = v; bi = i; }
+            }
+            sum += best; last = best; last_i = bi;
+        }
+        gs[g] = sum;
+    }
+    __syncwarp();
+    // the groups that stay: `keep` rounds of an arg-max over the groups' scores (lowest index on a tie); a group that was
+    // picked is marked by a score of +inf, which no sum of sigmoids and corrections reaches
+    for (int r = 0; r < keep; ++r) {
+        float best = -INFINITY; int bi = 0x7fffffff;
+        for (int g = lane; g < groups; g += 32) {
+            const float v = gs[g];
+            if (v != INFINITY && (bi == 0x7fffffff || v > best)) { best = v; bi = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+        }
+        if (lane == 0 && bi != 0x7fffffff) gs[bi] = INFINITY;
+        __syncwarp();
+    }
+    unsigned taken = 0;                                  // bit k: my element lane + 32 k is chosen
+    float mine = 0.f, sum = 0.f;                         // lane j keeps the j-th chosen expert's s
+    for (int j = 0; j < top; ++j) {
+        float best = -INFINITY; int bi = 0x7fffffff;
+        for (int k = 0, e = lane; e < E; ++k, e += 32) {
+            if (((taken >> k) & 1u) || gs[e / per] != INFINITY) continue;
+            const float v = c[e];
+            if (bi == 0x7fffffff || v > best) { best = v; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+        }
+        if (bi == 0x7fffffff) bi = 0;                    // fewer experts stay than `top` asks for (the launcher refuses that)
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        const float p = s[bi];
+        sum += p;
+        if (lane == j) mine = p;
+        if (lane == 0) idx[(size_t)t * top + j] = bi;
+    }
+    if (lane < top) wts[(size_t)t * top + lane] = mine / (sum + 1e-20f) * scale;
+}
+
+TL_EXPORT int tl_route_groups(const float* z, int ldz, const float* correction, int E, int top, int groups, int keep, int gtop,
+                              float scale, int* idx, float* wts, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E > 1024 || top > 32 || top < 1 || groups < 1 || E % groups || keep < 1 || keep > groups || gtop < 1 ||
+        top > keep * (E / groups)) return 1;
+    const size_t smem = ((size_t)2 * E + groups) * sizeof(float);
+    launch_after_wait(route_groups_kernel, dim3(T), dim3(32), smem, stream, z, ldz, correction, E, top, groups, keep, gtop, scale, idx, wts);
+    return tl_launch_status();
+}
+
 // ------------------------------------------------------------------ experts, few tokens
 constexpr int MOE_ROWS = 16;                             // output rows a block of moe_up (4 a warp, their loads in flight together)
 constexpr int MOE_DOWN_ROWS = 4;                         // output rows a block of moe_down (a warp an expert)
@@ -167,7 +259,7 @@ constexpr int MOE_DOWN_ROWS = 4;                         // output rows a block 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, const TW* __restrict__ w_up, const int* __restrict__ idx,
                                                      TA* __restrict__ a, int K, int F, int top, int gated, int act,
-                                                     const float* __restrict__ in_scale) {
+                                                     const float* __restrict__ in_scale, float limit, float alpha) {
     extern __shared__ __align__(16) float xs[];
     const int pair = blockIdx.x, t = pair / top, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
@@ -189,7 +281,7 @@ __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, c
 #pragma unroll
         for (int r = 0; r < 4; ++r)
             if (lane == 0 && f + r < f1)
-                a[(size_t)pair * F + f + r] = from_f<TA>(gated ? tl_act(sc * g[r], act) * (sc * u[r]) : tl_act(sc * u[r], act));
+                a[(size_t)pair * F + f + r] = from_f<TA>(gated ? tl_act_pair(sc * g[r], sc * u[r], act, limit, alpha) : tl_act(sc * u[r], act));
     }
 }
 
@@ -230,13 +322,14 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a,
 }
 
 TL_EXPORT int tl_moe_up(const void* h, int act_dtype, const void* w_up, int w_dtype, const int* idx, void* a, int P, int K,
-                        int F, int top, int gated, int act, const float* in_scale, cudaStream_t stream) {
+                        int F, int top, int gated, int act, const float* in_scale, float limit, float alpha, cudaStream_t stream) {
     if (P <= 0) return 0;
+    if (act == TL_ACT_SWISH_CLAMPED && !gated) return 1;
     const size_t smem = (size_t)K * sizeof(float);
     if (smem > 48 * 1024) return 1;
     const dim3 grid(P, (F + MOE_ROWS - 1) / MOE_ROWS);
     if (grid.y > 65535) return 1;
-#define MU(TA, TW) launch_after_wait(moe_up_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top, gated, act, in_scale)
+#define MU(TA, TW) launch_after_wait(moe_up_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top, gated, act, in_scale, limit, alpha)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MU(float, float); else MU(float, bf16); }
     else { if (w_dtype == TL_F32) MU(bf16, float); else MU(bf16, bf16); }
 #undef MU

@@ -16,11 +16,13 @@ from ..config.base import ConfigError, architecture_name, read_config_json
 from ..config.qwen2 import Qwen2Config
 from ..config.vutesun import VutesunConfig
 from ..config.dekerax import DekeraxConfig
+from ..config.sumuvik import SumuvikConfig
 from ..parts import Runtime
 from ..weights import load_weights
 from .qwen2 import describe_qwen2
 from .vutesun import describe_vutesun
 from .dekerax import describe_dekerax
+from .sumuvik import describe_sumuvik
 from .spec import Model
 
 
@@ -51,6 +53,7 @@ def registered_architectures() -> list:
 register_architecture("Qwen2ForCausalLM", Qwen2Config, describe_qwen2)
 register_architecture("Vutesun", VutesunConfig, describe_vutesun)
 register_architecture("Dekerax", DekeraxConfig, describe_dekerax)
+register_architecture("Sumuvik", SumuvikConfig, describe_sumuvik)
 
 
 def load_config(folder):

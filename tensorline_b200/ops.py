@@ -14,18 +14,20 @@ import torch
 from .csrc.build import CHECK_BUILD, load_library
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "attn_tokenwise.cu", "gemm_f32.cu", "sampling.cu", "recurrent.cu", "moe.cu",
-                "delta.cu", "latent.cu"]
+                "delta.cu", "latent.cu", "rglru.cu"]
 
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
 _SIGNATURES = {
-    "tl_embed": [_P, _P, _I, _P, _I, _I, _P],
+    "tl_embed": [_P, _P, _I, _P, _I, _I, _F, _P],
     "tl_add_rmsnorm": [_P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, _F, _I, _P],
-    "tl_silu_mul": [_P, _P, _I, _I, _I, _I, _I, _P],
+    "tl_silu_mul": [_P, _P, _I, _I, _I, _I, _I, _F, _F, _P],
+    "tl_add_rmsnorm_pair": [_P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _I, _I, _F, _P],
+    "tl_head_gate": [_P, _I, _P, _I, _I, _I, _P],
     "tl_post_norm_add_norm": [_P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P],
     "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong,
                          _I, _P, _P, _F, _I, _I, _P, _P],
-    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _I, _P, _P],
+    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _P, _I, _I, _P, _P],
     "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
     "tl_argmax": [_P, _I, _I, _I, _P, _P, _P],
     "tl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
@@ -37,7 +39,10 @@ _SIGNATURES = {
     "tl_sum_normed": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _F, _P],
     "tl_small_proj": [_P, _I, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "tl_topk_softmax": [_P, _I, _I, _I, _P, _P, _I, _I, _P],
-    "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
+    "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _F, _P],
+    "tl_route_groups": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P],
+    "tl_causal_conv": [_P, _I, _I, _P, _P, _P, _I, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _P],
+    "tl_rglru_scan": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
     "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
     "tl_moe_sort": [_P, _I, _I, _P, _P, _P, _P],
     "tl_moe_gather": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P],
@@ -244,13 +249,13 @@ def _ints(t: torch.Tensor, name: str) -> None:
 
 # ---------------------------------------------------------------------------------------------
 
-def embed(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
-    """x[t, :] = table[ids[t], :], x float32 [T, H]."""
+def embed(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> None:
+    """x[t, :] = table[ids[t], :] * scale, x float32 [T, H]."""
     T, H = x.shape
     if x.dtype != torch.float32 or table.shape[1] != H or ids.numel() != T:
         raise KernelError("embed: x must be float32 [T, H] matching the table and ids")
     _contig(x, "x"); _contig(table, "table"); _ints(ids, "ids")
-    _check(core().tl_embed(_ptr(x), _ptr(table), dtype_code(table.dtype), _ptr(ids), T, H, _stream()), "embed")
+    _check(core().tl_embed(_ptr(x), _ptr(table), dtype_code(table.dtype), _ptr(ids), T, H, float(scale), _stream()), "embed")
 
 
 def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: torch.Tensor, eps: float,
@@ -291,11 +296,25 @@ def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: t
            "add_rmsnorm")
 
 
-GATE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu_squared": 2}
+GATE_ACTS = {"silu": 0, "gelu_tanh": 1, "relu_squared": 2, "swish_clamped": 3}
 
 
-def silu_mul(gu: torch.Tensor, out: torch.Tensor, block: int | None = None, act: str = "silu") -> None:
-    """out = act(gate) * up from gu [T, 2I], act "silu" or "gelu_tanh" (the tanh form of gelu).  block None: gate = gu[:, :I], up = gu[:, I:]; else gate
+def gate_act(act) -> tuple:
+    """(code, limit, alpha) of an activation given by name, or as ("swish_clamped", limit, alpha): with g' = min(g, limit) and
+    u' = clamp(u, -limit, limit) the gated unit is g' sigmoid(alpha g') (u' + 1)."""
+    if isinstance(act, tuple):
+        name, limit, alpha = act
+        if name != "swish_clamped" or not limit > 0:
+            raise KernelError(f"an activation with constants is ('swish_clamped', limit > 0, alpha), not {act!r}")
+        return GATE_ACTS[name], float(limit), float(alpha)
+    if act not in GATE_ACTS or act == "swish_clamped":
+        raise KernelError(f"activation {act!r} is not one of {sorted(GATE_ACTS)} ('swish_clamped' comes with its constants)")
+    return GATE_ACTS[act], 0.0, 0.0
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor, block: int | None = None, act="silu") -> None:
+    """out = act(gate) * up from gu [T, 2I], act "silu", "gelu_tanh" (the tanh form of gelu) or ("swish_clamped", limit, alpha)
+    (see `gate_act`).  block None: gate = gu[:, :I], up = gu[:, I:]; else gate
     and up columns alternate in blocks of `block` columns (gate first), as a product against weight rows
     interleaved that way leaves them."""
     T, I = out.shape
@@ -305,9 +324,44 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor, block: int | None = None, act:
     if blk <= 0 or I % blk:
         raise KernelError(f"silu_mul: the block of {blk} columns must divide I = {I}")
     _contig(gu, "gu"); _contig(out, "out")
-    if act not in ("silu", "gelu_tanh"):
-        raise KernelError(f"silu_mul: act {act!r} is neither 'silu' nor 'gelu_tanh'")
-    _check(core().tl_silu_mul(_ptr(gu), _ptr(out), dtype_code(out.dtype), T, I, blk, GATE_ACTS[act], _stream()), "silu_mul")
+    code, limit, alpha = gate_act(act)
+    if code == GATE_ACTS["relu_squared"]:
+        raise KernelError("silu_mul: 'relu_squared' is not a gate of this kernel")
+    _check(core().tl_silu_mul(_ptr(gu), _ptr(out), dtype_code(out.dtype), T, I, blk, code, limit, alpha, _stream()), "silu_mul")
+
+
+def add_rmsnorm_pair(x: torch.Tensor, a: torch.Tensor | None, b: torch.Tensor | None, w1: torch.Tensor, w2: torch.Tensor | None,
+                     h1: torch.Tensor, h2: torch.Tensor | None, eps: float, rows: torch.Tensor | None = None) -> None:
+    """x += a + b (either may be None; b only with a), then h1 = x / rms(x) * w1 and h2 = x / rms(x) * w2 from one set of
+    statistics, float32 up to the rounding of h1 and h2.  x float32 [*, H]; a, b, h1, h2 of the activation type; `rows`
+    picks the rows that are produced (x is then left alone).  h2 and w2 None: one norm."""
+    H = x.shape[-1]
+    R = x.shape[0] if rows is None else rows.numel()
+    if x.dtype != torch.float32 or not x.is_contiguous() or h1.shape != (R, H) or not h1.is_contiguous():
+        raise KernelError("add_rmsnorm_pair: x must be contiguous float32 [*, H] and h1 [rows, H]")
+    if (h2 is None) != (w2 is None) or (b is not None and a is None):
+        raise KernelError("add_rmsnorm_pair: the second norm comes with its weight, the second addend with the first")
+    for name, t in (("a", a), ("b", b)):
+        if t is not None and (t.shape != x.shape or t.dtype != h1.dtype or not t.is_contiguous()):
+            raise KernelError(f"add_rmsnorm_pair: {name} must have x's shape and h1's type")
+    if h2 is not None and (h2.shape != h1.shape or h2.dtype != h1.dtype or not h2.is_contiguous()):
+        raise KernelError("add_rmsnorm_pair: h2 must be like h1")
+    for w in (w1, w2):
+        if w is not None and (w.numel() != H or w.dtype != w1.dtype or not w.is_contiguous()):
+            raise KernelError("add_rmsnorm_pair: weights must be [H] of one type")
+    if rows is not None:
+        _ints(rows, "rows")
+    _check(core().tl_add_rmsnorm_pair(_ptr(x), _ptr(a), _ptr(b), _ptr(w1), _ptr(w2), dtype_code(w1.dtype), _ptr(h1), _ptr(h2),
+                                      dtype_code(h1.dtype), _ptr(rows), R, H, float(eps), _stream()), "add_rmsnorm_pair")
+
+
+def head_gate(o: torch.Tensor, gate: torch.Tensor, nq: int, d: int) -> None:
+    """o[t, h, :] *= sigmoid(gate[t, h]) in place; o [T, nq * d] of the activation type, gate float32 [T, nq]."""
+    T = o.shape[0]
+    if o.shape != (T, nq * d) or gate.shape != (T, nq) or gate.dtype != torch.float32:
+        raise KernelError("head_gate: o [T, nq d], gate float32 [T, nq]")
+    _contig(o, "o"); _contig(gate, "gate")
+    _check(core().tl_head_gate(_ptr(o), dtype_code(o.dtype), _ptr(gate), T, nq, d, _stream()), "head_gate")
 
 
 def post_norm_add_norm(x: torch.Tensor, a: torch.Tensor | None, w_post: torch.Tensor | None, w_pre: torch.Tensor | None,
@@ -389,9 +443,11 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tenso
 
 def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                    table: torch.Tensor, page_size: int, pos: torch.Tensor, req_slot: torch.Tensor,
-                   nq: int, nkv: int, d: int, window: int | None, scale: float, sink: torch.Tensor | None = None) -> None:
+                   nq: int, nkv: int, d: int, window: int | None, scale: float, sink: torch.Tensor | None = None,
+                   keep_first: int = 0, gate: torch.Tensor | None = None) -> None:
     """Exact-order paged attention; q rows `q_stride` elements apart, out [T, nq*d].  `sink` (float32 [nq]): one more
-    term exp(sink[h]) in every softmax denominator of head h."""
+    term exp(sink[h]) in every softmax denominator of head h.  `keep_first` (with a window): the keys at positions below
+    it stay visible beside the window.  `gate` (float32 [T, nq]): the row of (t, h) is multiplied by sigmoid(gate[t, h])."""
     T = out.shape[0]
     if out.shape[1] != nq * d or out.dtype != q.dtype or k_pages.dtype != q.dtype:
         raise KernelError("attn_tokenwise: out must be [T, nq*d] and all tensors of one type")
@@ -400,10 +456,14 @@ def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: t
     _contig(out, "out"); _contig(k_pages, "k_pages"); _contig(v_pages, "v_pages")
     _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(table, "table")
     _sink(sink, nq, "attn_tokenwise")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape != (T, nq) or not gate.is_contiguous()):
+        raise KernelError("attn_tokenwise: gate must be float32 [T, query heads]")
+    if keep_first < 0:
+        raise KernelError("attn_tokenwise: keep_first must not be negative")
     _check(core().tl_attn_tokenwise(_ptr(q), q_stride, _ptr(out), dtype_code(q.dtype), _ptr(k_pages), _ptr(v_pages),
                                     _ptr(table), table.shape[1], page_size, _ptr(pos), _ptr(req_slot), T, nq, nkv, d,
-                                    int(window or 0), float(scale), _ptr(sink), table.shape[0], k_pages.shape[0], fault_words(out.device),
-                                    _stream()), "attn_tokenwise")
+                                    int(window or 0), float(scale), _ptr(sink), int(keep_first), _ptr(gate), table.shape[0],
+                                    k_pages.shape[0], fault_words(out.device), _stream()), "attn_tokenwise")
 
 
 def _sink(sink, nq: int, who: str) -> None:
@@ -582,7 +642,25 @@ def topk_softmax(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor
            "topk_softmax")
 
 
-def moe_up(h: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, a: torch.Tensor, act: str = "relu_squared",
+def route_groups(z: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int, keep: int, group_top: int, scale: float,
+                 idx: torch.Tensor, wts: torch.Tensor) -> None:
+    """Per row of z (float32 [T, E]): s = sigmoid(z); the choice scores are s + correction (float32 [E] or None).  The experts
+    form `groups` equal groups of neighbours; a group's score is the sum of its `group_top` largest choice scores; only the
+    experts of the `keep` best groups can be chosen.  idx int32 [T, top]: the `top` largest choice scores among them (lowest
+    index first on a tie); wts float32 [T, top]: the chosen experts' s divided by their sum (+ 1e-20), times `scale`."""
+    T, E = z.shape
+    if z.dtype != torch.float32 or wts.dtype != torch.float32 or idx.shape != (T, top) or wts.shape != (T, top) or z.stride(1) != 1:
+        raise KernelError("route_groups: z float32 [T, E], idx int32 [T, top], wts float32 [T, top]")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E or not correction.is_contiguous()):
+        raise KernelError("route_groups: correction must be float32 [E]")
+    if groups < 1 or E % groups or not 1 <= keep <= groups or group_top < 1 or top > keep * (E // groups):
+        raise KernelError(f"route_groups: {E} experts in {groups} groups, {keep} kept, top {top}")
+    _ints(idx, "idx"); _contig(wts, "wts")
+    _check(core().tl_route_groups(_ptr(z), z.stride(0), _ptr(correction), E, int(top), int(groups), int(keep), int(group_top),
+                                  float(scale), _ptr(idx), _ptr(wts), T, _stream()), "route_groups")
+
+
+def moe_up(h: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, a: torch.Tensor, act="relu_squared",
            gated: bool = False, in_scale: torch.Tensor | None = None) -> None:
     """a[t * top + j, :] = act(s w_up[idx[t, j]] h[t]); w_up [E, F, K], a [T * top, F] of h's type; s = in_scale[t, j]
     (float32 [T, top]: the weight on the expert's input) or 1.  `gated`: w_up is [E, 2F, K], an expert's gate rows then its up
@@ -592,13 +670,12 @@ def moe_up(h: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, a: torch.Tens
     F = a.shape[1]
     if w_up.dim() != 3 or w_up.shape[1:] != ((2 * F if gated else F), K) or a.shape != (T * top, F) or a.dtype != h.dtype:
         raise KernelError("moe_up: w_up [E, F, K] ([E, 2F, K] gated), a [T top, F] of h's type")
-    if act not in GATE_ACTS:
-        raise KernelError(f"moe_up: act {act!r} is not one of {sorted(GATE_ACTS)}")
+    code, limit, alpha = gate_act(act)
     if in_scale is not None and (in_scale.dtype != torch.float32 or in_scale.shape != idx.shape or not in_scale.is_contiguous()):
         raise KernelError("moe_up: in_scale must be float32 [T, top]")
     _contig(h, "h"); _contig(w_up, "w_up"); _ints(idx, "idx"); _contig(a, "a")
     _check(core().tl_moe_up(_ptr(h), dtype_code(h.dtype), _ptr(w_up), dtype_code(w_up.dtype), _ptr(idx), _ptr(a), T * top, K, F,
-                            top, int(gated), GATE_ACTS[act], _ptr(in_scale), _stream()), "moe_up")
+                            top, int(gated), code, _ptr(in_scale), limit, alpha, _stream()), "moe_up")
 
 
 def _extra(extra, gate, y, who):
@@ -801,3 +878,59 @@ def head_matmul(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, H: int, K: in
     _contig(w, "w")
     _check(core().tl_head_matmul(_ptr(x), x.stride(0), x_head_stride, _ptr(w), dtype_code(w.dtype), _ptr(y), y.stride(0),
                                  y_head_stride, T, H, K, N, dtype_code(x.dtype), _stream()), "head_matmul")
+
+
+# ---------------------------------------------------------------------------------------------
+# The real-gated linear recurrent unit and its short convolution (csrc/rglru.cu)
+
+def causal_conv(proj: torch.Tensor, off: int, in_bias: torch.Tensor | None, W: int, taps_w: torch.Tensor, out_bias: torch.Tensor | None,
+                conv_state: torch.Tensor | None, q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, *, B: int,
+                max_q_len: int) -> None:
+    """out[t, c] = out_bias[c] + sum_k taps_w[c, k] x[t - (taps - 1) + k, c] with x = proj[:, off + c] + in_bias[off + c], a causal
+    convolution over a request's tokens per channel (the last tap on the current token).  The taps - 1 inputs before the
+    step come from `conv_state[slot]` (float32 [taps - 1, W], zero for a new request), which is then brought up to date.
+    proj float32 [T, >= off + W], taps_w float32 [W, taps], out float32 [T, W]."""
+    T = proj.shape[0]
+    taps = taps_w.shape[1]
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < off + W or out.shape != (T, W) or out.dtype != torch.float32:
+        raise KernelError("causal_conv: proj float32 [T, >= off + W], out float32 [T, W]")
+    if taps_w.shape != (W, taps) or taps_w.dtype != torch.float32:
+        raise KernelError("causal_conv: taps_w must be float32 [W, taps]")
+    for name, t, n in (("in_bias", in_bias, off + W), ("out_bias", out_bias, W)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() < n or not t.is_contiguous()):
+            raise KernelError(f"causal_conv: {name} must be float32 with {n} entries")
+    _contig(taps_w, "taps_w"); _contig(out, "out"); _ints(q_start, "q_start"); _ints(slots, "slots")
+    slot_stride = 0
+    if taps > 1:
+        if conv_state is None or conv_state.dtype != torch.float32 or not conv_state.is_contiguous() or \
+                conv_state[0].numel() != (taps - 1) * W:
+            raise KernelError("causal_conv: conv_state must be float32 [slots, (taps - 1) * W]")
+        slot_stride = conv_state[0].numel()
+    _check(core().tl_causal_conv(_ptr(proj), proj.stride(0), int(off), _ptr(in_bias), _ptr(taps_w), _ptr(out_bias), taps,
+                                 _ptr(conv_state) if taps > 1 else None, slot_stride, _ptr(q_start), _ptr(slots), _ptr(out), int(B),
+                                 int(max_q_len), int(W), _stream()), "causal_conv", launches=2 if taps > 1 else 1)
+
+
+def rglru_scan(gates: torch.Tensor, gate_bias: torch.Tensor, u: torch.Tensor, proj: torch.Tensor, in_bias: torch.Tensor | None,
+               lam: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, *, B: int,
+               blocks: int, sharpness: float, max_q_len: int, y_off: int = 0) -> None:
+    """Per (request, channel c), tokens in order, from the state in `state[slot]` (float32 [W], left up to date):
+    r = sigmoid(zr + br), i = sigmoid(zi + bi), log a = -sharpness r softplus(lam[c]), S <- exp(log a) S + sqrt(1 - a^2) i u[t, c],
+    out[t, c] = S gelu_tanh(proj[t, y_off + c] + in_bias[y_off + c]).  gates float32 [T, 2W]: for each of the `blocks` equal
+    parts of the channels its r pre-activations, then its i pre-activations; gate_bias float32 laid out alike."""
+    T, W = u.shape
+    if gates.shape != (T, 2 * W) or gates.dtype != torch.float32 or u.dtype != torch.float32 or out.shape != (T, W):
+        raise KernelError("rglru_scan: gates float32 [T, 2W], u float32 [T, W], out [T, W]")
+    if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < y_off + W or proj.shape[0] != T:
+        raise KernelError("rglru_scan: proj float32 [T, >= y_off + W]")
+    if W % blocks or gate_bias.numel() != 2 * W or gate_bias.dtype != torch.float32 or lam.numel() != W or lam.dtype != torch.float32:
+        raise KernelError("rglru_scan: gate_bias float32 [2W], lam float32 [W], W a multiple of blocks")
+    if in_bias is not None and (in_bias.dtype != torch.float32 or in_bias.numel() < y_off + W):
+        raise KernelError("rglru_scan: in_bias must be float32 with y_off + W entries")
+    if state.dtype != torch.float32 or state[0].numel() != W:
+        raise KernelError("rglru_scan: a slot holds W floats")
+    _contig(gates, "gates"); _contig(gate_bias, "gate_bias"); _contig(u, "u"); _contig(lam, "lam"); _contig(state, "state")
+    _contig(out, "out"); _ints(q_start, "q_start"); _ints(slots, "slots")
+    _check(core().tl_rglru_scan(_ptr(gates), _ptr(gate_bias), _ptr(u), _ptr(proj), proj.stride(0), int(y_off), _ptr(in_bias), _ptr(lam),
+                                _ptr(state), _ptr(q_start), _ptr(slots), _ptr(out), dtype_code(out.dtype), int(B), W, int(blocks),
+                                float(sharpness), int(max_q_len), _stream()), "rglru_scan")

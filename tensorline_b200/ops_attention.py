@@ -331,11 +331,17 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
                                       _stream()), "attn_decode" + ("+combine" if splits > 1 else ""), launches=2 if splits > 1 else 1)
 
 
-def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale, rope: dict | None = None, sink=None) -> None:
+TAKES_KEEP_FIRST = False            # whether the tensor-core kernels read kept first keys beside a window
+
+
+def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale, rope: dict | None = None, sink=None,
+                keep_first: int = 0) -> None:
     """`rope`: only for decode-only steps that `decode_takes_rope` accepted (see `decode`).  `sink`: float32 [nq], one more
     term exp(sink[h]) in the softmax denominators of head h (every kernel adds it once, where a row is finished)."""
     if qkv.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
         raise KernelError("attend_bf16: bfloat16 tensors only")
+    if keep_first and window and not TAKES_KEEP_FIRST:
+        raise KernelError("attend_bf16: these kernels do not read kept first keys beside a window")
     q_stride = qkv.shape[1]
     if rope is not None and not ctx.decode_only:
         raise KernelError("attend_bf16: the rotary step folds into decode-only steps")

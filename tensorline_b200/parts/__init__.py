@@ -3,5 +3,5 @@ from .base import (PartSpec, Runtime, Part, Registry, Rotary, NORMS, POSITION_EN
                    EMBEDDINGS, HEADS, register_norm, register_position_encoding, register_mixer,
                    register_feed_forward, register_block, register_embedding, register_head, KVCacheView,
                    StateView, TensorSpec, tensor_name)
-from . import norm, rope, mlp, attention, block, recurrent, parallel, moe, latent, delta          # noqa: F401  (registration)
+from . import norm, rope, mlp, attention, block, recurrent, parallel, moe, latent, delta, rglru   # noqa: F401  (registration)
 from .embedding import Embedding, LMHead

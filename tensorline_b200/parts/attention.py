@@ -19,6 +19,12 @@ than queries and keys) and `names` (the tensors' names under the mixer's prefix)
 on one head size: with `v_head_dim` != `head_dim`, or a size the bfloat16 kernels do not take, the smaller of
 q/k and v is padded with zero rows in the stacked projection (and zero columns in the output projection), which
 changes no score and no output.
+
+`keep_first` (with a window): the first `keep_first` positions of the request stay visible to every later query beside
+its window, at their true positions.  `sink_value`: the sink is this fixed number for every head instead of a tensor
+(0.0: the denominator holds one more term 1).  `head_gate` (tensor `head_gate`, [query heads, hidden]): head h's output
+is multiplied by sigmoid(W_g x)_h, one number per token and head computed in float32 from the mixer's input, before the
+output projection.
 """
 from __future__ import annotations
 
@@ -27,11 +33,11 @@ import torch
 from .. import ops
 from ..cache import PagedKV
 from .base import POSITION_ENCODINGS, Part, PartSpec, Rotary, Runtime, TensorSpec, register_mixer
-from .linear import SplitSum, matmul
+from .linear import SplitSum, matmul, resolve
 
 _NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
           "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "v_bias": "v_proj.bias",
-          "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sink"}
+          "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sink", "head_gate": "gate"}
 
 
 def _pad_heads(t: torch.Tensor, heads: int, size: int, to: int) -> torch.Tensor:
@@ -52,7 +58,7 @@ class PagedAttention(Part):
     def __init__(self, rt: Runtime, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, position: PartSpec, window: int | None = None, scale: float | None = None,
                  qk_norm_eps: float | None = None, v_head_dim: int | None = None, sink: bool = False,
-                 names: dict | None = None):
+                 names: dict | None = None, keep_first: int = 0, sink_value: float | None = None, head_gate: bool = False):
         super().__init__(rt)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
@@ -65,15 +71,19 @@ class PagedAttention(Part):
             raise ValueError("a q/k norm over a padded head is not supported")
         self.hidden, self.nq, self.nkv, self.d = hidden, num_heads, num_kv_heads, d
         self.qkv_bias, self.window = qkv_bias, window
+        self.keep_first = int(keep_first) if window is not None else 0
+        if sink and sink_value is not None:
+            raise ValueError("a sink is either a tensor or a fixed number")
+        self.sink_value, self.head_gate = sink_value, bool(head_gate)
         self.scale = head_dim ** -0.5 if scale is None else scale          # tensorline/paged.py:119
         self.position = POSITION_ENCODINGS.build(position, rt, head_dim=head_dim)
         self.qk_norm_eps = qk_norm_eps
         self.has_sink = bool(sink)
         self.names = {**_NAMES, **(names or {})}
-        self.w_qkv = self.b_qkv = self.w_o = self.q_norm = self.k_norm = self.sink = None
+        self.w_qkv = self.b_qkv = self.w_o = self.q_norm = self.k_norm = self.sink = self.w_gate = None
 
     def cache_need(self):
-        return PagedKV(self.nkv, self.d, self.window)
+        return PagedKV(self.nkv, self.d, self.window, keep_first=self.keep_first)
 
     def expected_tensors(self, prefix):
         H, nq, nkv, dk, dv = self.hidden, self.nq, self.nkv, self.dk, self.dv
@@ -87,6 +97,8 @@ class PagedAttention(Part):
             out.update({n["q_norm"]: TensorSpec((dk,), init="ones"), n["k_norm"]: TensorSpec((dk,), init="ones")})
         if self.has_sink:
             out[n["sink"]] = TensorSpec((nq,))
+        if self.head_gate:
+            out[n["head_gate"]] = TensorSpec((nq, H))
         return out
 
     def bind(self, weights, prefix):
@@ -107,10 +119,19 @@ class PagedAttention(Part):
             self.k_norm = weights[n["k_norm"]].float().contiguous()
         if self.has_sink:
             self.sink = weights[n["sink"]].float().contiguous()
+        elif self.sink_value is not None:
+            self.sink = torch.full((nq,), float(self.sink_value), dtype=torch.float32, device=self.w_o.device)
+        if self.head_gate:
+            self.w_gate = weights[n["head_gate"]].contiguous()      # stored type; the gate's product accumulates in float32
 
     def forward(self, h, ctx, cache):
         nq, nkv, d = self.nq, self.nkv, self.d
         T = h.shape[0]
+        gate = None
+        if self.w_gate is not None:                      # one number per token and head, float32
+            h = resolve(h)
+            gate = torch.empty((T, nq), dtype=torch.float32, device=h.device)
+            ops.small_proj(h, self.w_gate, None, gate)
         rotary = self.position.rotary()
         if not isinstance(rotary, Rotary):               # a plain (inv_freq, rot) pair means rotate-half pairing
             rotary = Rotary(*rotary)
@@ -137,13 +158,13 @@ class PagedAttention(Part):
         else:
             rotary_kernel()
         o = torch.empty((T, nq * d), dtype=qkv.dtype, device=h.device)
-        self.attend(qkv, o, ctx, cache, table, rope=fold)
+        self.attend(qkv, o, ctx, cache, table, rope=fold, gate=gate)
         return matmul(o, self.w_o, may_defer=True, to_residual=True)     # the block's next norm adds it up
 
     def _folds_rope(self, ctx) -> bool:
         from .. import ops_attention
         return ops_attention.decode_takes_rope(ctx.B, self.d, ctx.page_size)
 
-    def attend(self, qkv, o, ctx, cache, table, rope=None):
+    def attend(self, qkv, o, ctx, cache, table, rope=None, gate=None):
         from . import attention_kernels
-        attention_kernels.attend(self, qkv, o, ctx, cache, table, rope=rope)
+        attention_kernels.attend(self, qkv, o, ctx, cache, table, rope=rope, gate=gate)

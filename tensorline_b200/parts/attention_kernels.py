@@ -12,12 +12,19 @@ import torch
 from .. import ops
 
 
-def attend(mixer, qkv, o, ctx, cache, table, rope=None) -> None:
+def attend(mixer, qkv, o, ctx, cache, table, rope=None, gate=None) -> None:
+    """`gate` (float32 [T, query heads]): head h's output of token t is multiplied by sigmoid(gate[t, h]); the exact-order
+    kernel does it where it writes a row, the tensor-core kernels are followed by a kernel that does."""
     nq, nkv, d = mixer.nq, mixer.nkv, mixer.d
     sink = getattr(mixer, "sink", None)
-    if qkv.dtype == torch.float32 or ctx.force_exact_attention or d > 256:     # heads wider than the tensor-core kernels take
-        ops.attn_tokenwise(qkv, qkv.shape[1], o, cache.k, cache.v, table, ctx.page_size, ctx.pos, ctx.req_slot,
-                           nq, nkv, d, mixer.window, mixer.scale, sink=sink)
-        return
+    keep_first = getattr(mixer, "keep_first", 0) if mixer.window else 0
     from .. import ops_attention
-    ops_attention.attend_bf16(qkv, o, ctx, cache.k, cache.v, table, nq, nkv, d, mixer.window, mixer.scale, rope=rope, sink=sink)
+    if qkv.dtype == torch.float32 or ctx.force_exact_attention or d > 256 or \
+            (keep_first and not ops_attention.TAKES_KEEP_FIRST):                # heads wider than the tensor-core kernels take
+        ops.attn_tokenwise(qkv, qkv.shape[1], o, cache.k, cache.v, table, ctx.page_size, ctx.pos, ctx.req_slot,
+                           nq, nkv, d, mixer.window, mixer.scale, sink=sink, keep_first=keep_first, gate=gate)
+        return
+    ops_attention.attend_bf16(qkv, o, ctx, cache.k, cache.v, table, nq, nkv, d, mixer.window, mixer.scale, rope=rope, sink=sink,
+                              keep_first=keep_first)
+    if gate is not None:
+        ops.head_gate(o, gate, nq, d)

@@ -9,7 +9,7 @@ first norm (or the model's last) as `pending`.
 from __future__ import annotations
 
 from .base import FEED_FORWARDS, MIXERS, NORMS, Part, PartSpec, Runtime, register_block
-from .linear import PostNormed, Scaled, resolve
+from .linear import PairSum, PostNormed, Scaled, resolve
 
 
 @register_block("pre_norm")
@@ -77,6 +77,24 @@ class PreNormBlock(Part):
         if getattr(consumer, "accepts_normed_input", False) and getattr(norm, "can_defer", False):
             return norm.add_norm(x, pending, defer=True)
         return norm.add_norm(x, pending)
+
+
+@register_block("parallel_residual")
+class ParallelResidualBlock(PreNormBlock):
+    """A block whose mixer and feed-forward read the same stream, each through a norm of its own, and whose outputs join
+    it together:
+
+        x += mixer(norm1(x)) + feed_forward(norm2(x))
+
+    The two norms share their statistics and are one kernel, which also adds the pair of outputs of the block in front
+    (a `PairSum`) into the stream, in float32."""
+
+    def forward(self, x, pending, ctx, cache):
+        h1, h2 = self.norm1.add_norm_pair(x, pending, self.norm2 if self.ff is not None else None)
+        a = resolve(self.mixer.forward(h1, ctx, cache))
+        if self.ff is None:
+            return a
+        return PairSum(a, self.ff.forward(h2, ctx))
 
 
 @register_block("sandwich_norm")

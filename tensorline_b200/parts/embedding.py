@@ -12,9 +12,10 @@ from .linear import matmul
 class Embedding(Part):
     graph_capturable = True
 
-    def __init__(self, rt: Runtime, vocab: int, dim: int, tensor: str = "weight"):
+    def __init__(self, rt: Runtime, vocab: int, dim: int, tensor: str = "weight", scale: float = 1.0):
+        """`scale`: every row is multiplied by it on its way into the stream (in float32; a tied head reads the table itself)."""
         super().__init__(rt)
-        self.vocab, self.dim, self.tensor = vocab, dim, tensor
+        self.vocab, self.dim, self.tensor, self.scale = vocab, dim, tensor, float(scale)
         self.weight = None
 
     def expected_tensors(self, prefix):
@@ -26,7 +27,7 @@ class Embedding(Part):
     def forward(self, ids):
         """The residual stream starts here, in float32."""
         x = torch.empty((ids.numel(), self.dim), dtype=torch.float32, device=ids.device)
-        ops.embed(x, self.weight, ids)
+        ops.embed(x, self.weight, ids, scale=self.scale)
         return x
 
 

@@ -139,6 +139,15 @@ class PostNormed:
         return x.to(self.dtype)
 
 
+class PairSum:
+    """An addend of the residual stream that is the sum of two sub-blocks' outputs (a block whose mixer and feed-forward read
+    the same stream): x += a + b.  The norm that does the sum adds both in float32 in its kernel; anyone else calls `resolve`."""
+
+    def __init__(self, a, b):
+        self.a, self.b = resolve(a), resolve(b)
+        self.dtype, self.shape = self.a.dtype, self.a.shape
+
+
 def with_row(x: torch.Tensor, pending, row: torch.Tensor, eps: float):
     """`pending` with one more addend: the float32 vector `row`, added once to every row of the stream x."""
     if pending is None:
@@ -159,6 +168,8 @@ def resolve(t):
         return t.materialize()
     if isinstance(t, Scaled):
         return (t.value.float() * t.alpha).to(t.dtype)
+    if isinstance(t, PairSum):
+        return (t.a.float() + t.b.float()).to(t.dtype)
     if isinstance(t, PendingProduct):
         t = t.run()
     if isinstance(t, NormedInput):

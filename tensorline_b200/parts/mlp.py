@@ -1,4 +1,6 @@
 """Dense gated feed-forward: y = (act(h Wg^T) * (h Wu^T)) Wd^T, act = silu or the tanh form of gelu, no biases.
+A third activation, `swish_clamped`, works on the pair: with g' = min(g, limit) and u' = clamp(u, -limit, limit) the unit
+is g' sigmoid(alpha g') (u' + 1); `act_limit` and `act_alpha` are its constants.
 
 tzar-beep/Tensorline calls the installed package's module for this (tensorline/paged.py:276;
 shapes tensorline/manager.py:53-54).  Here gate and up are one product against the stacked
@@ -21,12 +23,17 @@ class GatedMLP(Part):
     graph_capturable = True
     accepts_normed_input = True         # `h` may be a `NormedInput`: the gate|up product normalises it on the fly
 
-    def __init__(self, rt: Runtime, hidden: int, intermediate: int, activation: str = "silu", names: dict | None = None):
+    def __init__(self, rt: Runtime, hidden: int, intermediate: int, activation: str = "silu", names: dict | None = None,
+                 act_limit: float | None = None, act_alpha: float = 1.0):
         """`names`: the three tensors' names under the part's prefix (keys gate, up, down)."""
         super().__init__(rt)
-        if activation not in ("silu", "gelu_tanh"):
-            raise ValueError(f"gated_mlp runs 'silu' or 'gelu_tanh', not {activation!r}")
+        if activation not in ("silu", "gelu_tanh", "swish_clamped"):
+            raise ValueError(f"gated_mlp runs 'silu', 'gelu_tanh' or 'swish_clamped', not {activation!r}")
+        if (activation == "swish_clamped") != (act_limit is not None):
+            raise ValueError("gated_mlp: 'swish_clamped' comes with act_limit, and only it")
         self.hidden, self.intermediate, self.activation = hidden, intermediate, activation
+        # what the kernels take: the activation's name, or (name, limit, alpha)
+        self.gate = activation if act_limit is None else (activation, float(act_limit), float(act_alpha))
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **(names or {})}
         self.w_gate_up = self.w_down = None
 
@@ -55,15 +62,15 @@ class GatedMLP(Part):
         if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_tc(h.shape[0], 2 * I, self.hidden):
             from .. import ops_gemm
             if ops_gemm.can_gate(h.shape[0], 2 * I, self.hidden):          # the activation inside the product
-                m = ops_gemm.gemm_tc(h, self.w_gate_up, gated=self.activation)
+                m = ops_gemm.gemm_tc(h, self.w_gate_up, gated=self.gate)
                 return matmul(m, self.w_down, may_defer=True, to_residual=True)
         if isinstance(h, NormedInput):                   # only the few-token products above take the recipe
             h = h.materialize()
         if self.block and h.dtype == torch.bfloat16 and h.is_contiguous() and use_pair_product(h.shape[0], 2 * I, self.hidden):
             from .. import ops_gemm
-            m = ops_gemm.gemm_tc2(h, self.w_gate_up, gated=self.activation)          # long steps: pairs of blocks, activation in the epilogue
+            m = ops_gemm.gemm_tc2(h, self.w_gate_up, gated=self.gate)          # long steps: pairs of blocks, activation in the epilogue
             return matmul(m, self.w_down, may_defer=True)
         gu = matmul(h, self.w_gate_up)
         m = torch.empty((h.shape[0], I), dtype=h.dtype, device=h.device)
-        ops.silu_mul(gu, m, block=self.block, act=self.activation)
+        ops.silu_mul(gu, m, block=self.block, act=self.gate)
         return matmul(m, self.w_down, may_defer=True, to_residual=True)          # the next norm adds it up

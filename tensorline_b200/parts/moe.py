@@ -9,7 +9,15 @@ the activation (`relu_squared`, `silu`, `gelu_tanh`), the weights as the sigmoid
 over the chosen (`scoring` "sigmoid": not renormalised), the weight on the expert's input instead of its output
 (`weight_on` "input": y = sum_j expert_j(weight_j h), which differs because an expert is not linear), no router bias, and a
 shared expert (`shared_inner`: one more gated unit of that size that every token runs, multiplied by sigmoid(w_sg . h), one
-number a token; its row `sg` rides in the router's product).
+number a token; its row `sg` rides in the router's product; `shared_gate` False: added as it is; `shared_act_limit`: the
+limit of its activation where that differs from the experts').
+
+`scoring` "sigmoid_share" is the choice among groups: s = sigmoid(z); the choice scores are s + `correction` (a tensor of
+one number an expert, `correction` True); the experts form `groups` equal groups of neighbours, a group's score is the sum
+of its `group_score_top` largest choice scores, and only experts of the `keep_groups` best groups can be chosen (the
+others count as minus infinity); the `top` largest choice scores among them are chosen, and their weights are their s
+(without the correction) divided by the sum of the chosen s (+ 1e-20), times `route_scale`.  The activation
+`swish_clamped` comes with `act_limit` and `act_alpha` (see parts/mlp.py).
 
 The experts' matrices are stacked ([E, F, K] and [E, K, F]) at load time.  Steps of few tokens stream, for every
 (token, chosen expert) pair, that expert's rows (`ops.moe_up`, `ops.moe_down`): nothing is sorted and nothing comes
@@ -39,23 +47,40 @@ class RoutedExperts(Part):
 
     def __init__(self, rt: Runtime, hidden: int, inner: int, experts: int, top: int, activation: str = "relu_squared",
                  router_bias: bool = True, names: dict | None = None, gated: bool = False, scoring: str = "softmax_chosen",
-                 weight_on: str = "output", shared_inner: int | None = None):
+                 weight_on: str = "output", shared_inner: int | None = None, shared_gate: bool = True,
+                 act_limit: float | None = None, act_alpha: float = 1.0, shared_act_limit: float | None = None,
+                 correction: bool = False, groups: int = 1, keep_groups: int = 1, group_score_top: int = 2,
+                 route_scale: float = 1.0):
         super().__init__(rt)
         if activation not in ops.GATE_ACTS:
             raise ValueError(f"routed_experts runs one of {sorted(ops.GATE_ACTS)}, not {activation!r}")
-        if scoring not in ("softmax_chosen", "sigmoid") or weight_on not in ("output", "input"):
+        if scoring not in ("softmax_chosen", "sigmoid", "sigmoid_share") or weight_on not in ("output", "input"):
             raise ValueError(f"routed_experts: scoring {scoring!r} / weight_on {weight_on!r} are not known")
         if not 1 <= top <= min(experts, 32) or experts > 1024:
             raise ValueError(f"routed_experts: top {top} of {experts} experts is outside what the choice kernel takes")
+        if (activation == "swish_clamped") != (act_limit is not None) or (activation == "swish_clamped" and not gated):
+            raise ValueError("routed_experts: 'swish_clamped' is a gated unit and comes with act_limit, and only it")
+        grouped = scoring == "sigmoid_share"
+        if not grouped and (correction or groups != 1 or route_scale != 1.0):
+            raise ValueError("routed_experts: a correction, groups and a scale of the weights belong to scoring 'sigmoid_share'")
+        if grouped and (groups < 1 or experts % groups or not 1 <= keep_groups <= groups or group_score_top < 1
+                        or top > keep_groups * (experts // groups)):
+            raise ValueError(f"routed_experts: {experts} experts in {groups} groups, {keep_groups} kept, top {top}")
         self.hidden, self.inner, self.E, self.top, self.router_bias = hidden, inner, experts, top, router_bias
         self.activation, self.gated, self.scoring, self.weight_on = activation, bool(gated), scoring, weight_on
+        self.act = activation if act_limit is None else (activation, float(act_limit), float(act_alpha))
+        self.has_correction, self.groups, self.keep_groups = bool(correction), int(groups), int(keep_groups)
+        self.group_score_top, self.route_scale = int(group_score_top), float(route_scale)
         self.names = {"router": "router", "router_bias": "router.b", "expert": "e{}", "up": "up", "down": "down", "gate": "gate",
-                      "shared": "shared", "shared_gate": "shared.sg", **(names or {})}
+                      "shared": "shared", "shared_gate": "shared.sg", "correction": "correction", **(names or {})}
         self.shared = None
+        self.shared_gate = bool(shared_gate) and shared_inner is not None
+        self.correction = None
         if shared_inner is not None:
             from .mlp import GatedMLP
-            self.shared = GatedMLP(rt, hidden, shared_inner, activation,
-                                   {k: self.names[k] for k in ("gate", "up", "down")})
+            limit = act_limit if shared_act_limit is None else shared_act_limit
+            self.shared = GatedMLP(rt, hidden, shared_inner, activation, {k: self.names[k] for k in ("gate", "up", "down")},
+                                   act_limit=limit, act_alpha=act_alpha)
         self.w_router = self.b_router = self.w_up = self.w_down = None
 
     def _expert(self, prefix, e, which):
@@ -72,7 +97,10 @@ class RoutedExperts(Part):
             out[self._expert(prefix, e, "down")] = TensorSpec((self.hidden, self.inner))
         if self.shared is not None:
             out.update(self.shared.expected_tensors(f"{prefix}.{self.names['shared']}"))
-            out[f"{prefix}.{self.names['shared_gate']}"] = TensorSpec((1, self.hidden))
+            if self.shared_gate:
+                out[f"{prefix}.{self.names['shared_gate']}"] = TensorSpec((1, self.hidden))
+        if self.has_correction:
+            out[f"{prefix}.{self.names['correction']}"] = TensorSpec((self.E,))
         return out
 
     def bind(self, weights, prefix):
@@ -81,6 +109,9 @@ class RoutedExperts(Part):
             self.b_router = weights[f"{prefix}.{self.names['router_bias']}"].to(w_router.dtype)
         if self.shared is not None:                      # the shared expert's gate is one more row of the router's product
             self.shared.bind(weights, f"{prefix}.{self.names['shared']}")
+        if self.has_correction:
+            self.correction = weights[f"{prefix}.{self.names['correction']}"].float().contiguous()
+        if self.shared_gate:
             w_router = torch.cat([w_router, weights[f"{prefix}.{self.names['shared_gate']}"].to(w_router.dtype).view(1, -1)])
             if self.b_router is not None:
                 self.b_router = torch.cat([self.b_router, self.b_router.new_zeros(1)])
@@ -102,15 +133,19 @@ class RoutedExperts(Part):
         ops.small_proj(h, self.w_router, self.b_router, z)
         idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
         wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
-        ops.topk_softmax(z[:, :E], top, idx, wts, scoring=self.scoring)
+        if self.scoring == "sigmoid_share":
+            ops.route_groups(z[:, :E], self.correction, top, self.groups, self.keep_groups, self.group_score_top, self.route_scale,
+                             idx, wts)
+        else:
+            ops.topk_softmax(z[:, :E], top, idx, wts, scoring=self.scoring)
         extra = extra_gate = None
         if self.shared is not None:
-            extra, extra_gate = resolve(self.shared.forward(h, ctx)), z[:, E]
+            extra, extra_gate = resolve(self.shared.forward(h, ctx)), (z[:, E] if self.shared_gate else None)
         on_input = self.weight_on == "input"
         y = torch.empty((T, self.hidden), dtype=h.dtype, device=h.device)
         if T <= STREAM_MAX_TOKENS or ctx.graph_max_ctx or self.rt.exact:
             a = torch.empty((T * top, self.inner), dtype=h.dtype, device=h.device)
-            ops.moe_up(h, self.w_up, idx, a, act=self.activation, gated=self.gated, in_scale=wts if on_input else None)
+            ops.moe_up(h, self.w_up, idx, a, act=self.act, gated=self.gated, in_scale=wts if on_input else None)
             ops.moe_down(a, self.w_down, idx, None if on_input else wts, y, extra=extra, extra_gate=extra_gate)
             return y
         offsets, place_of, pair_at = ops.moe_sort(idx, E)
@@ -123,7 +158,7 @@ class RoutedExperts(Part):
         ops.mark("library product")
         if self.gated:
             act = torch.empty((E * cap, self.inner), dtype=h.dtype, device=h.device)
-            ops.silu_mul(inner.view(E * cap, 2 * self.inner), act, act=self.activation)
+            ops.silu_mul(inner.view(E * cap, 2 * self.inner), act, act=self.act)
             inner = act.view(E, cap, self.inner)
         elif self.activation == "relu_squared":
             ops.relu_square(inner)

@@ -5,7 +5,7 @@ import torch
 
 from .. import ops
 from .base import Part, Runtime, TensorSpec, register_norm, tensor_name
-from .linear import FUSE_NORMS, NormedInput, PendingProduct, PostNormed, Scaled, SplitSum, resolve
+from .linear import FUSE_NORMS, NormedInput, PairSum, PendingProduct, PostNormed, Scaled, SplitSum, resolve
 
 
 @register_norm("rms_norm")
@@ -37,9 +37,32 @@ class RMSNorm(Part):
         ops.add_rmsnorm(x, None, self.weight, out, self.eps, cast_first=False)
         return out
 
+    def add_norm_pair(self, x, pending, other: "RMSNorm | None", rows=None):
+        """x += pending (a tensor, a `PairSum` or None), then this norm and `other`'s of the same rows of x with one set
+        of statistics: (h, h_other); float32 up to the weights, the results rounded once.  `other` None: (h, None)."""
+        if self.cast_first or self.one_plus or (other is not None and (other.cast_first or other.one_plus or other.eps != self.eps
+                                                                      or other.weight.dtype != self.weight.dtype)):
+            raise NotImplementedError("two norms of one stream share a kernel only as plain float32 norms with one eps")
+        a = b = None
+        if isinstance(pending, PairSum):
+            a, b = pending.a, pending.b
+        elif pending is not None:
+            a = resolve(pending)
+        n = x.shape[0] if rows is None else rows.numel()
+        h = torch.empty((n, self.dim), dtype=self.rt.act_dtype, device=x.device)
+        h2 = torch.empty_like(h) if other is not None else None
+        ops.add_rmsnorm_pair(x, a, b, self.weight, None if other is None else other.weight, h, h2, self.eps, rows=rows)
+        return h, h2
+
     def add_norm(self, x, pending, rows=None, defer=False):
         """`defer`: the caller's next step is a product that takes a `NormedInput`."""
         n = x.shape[0] if rows is None else rows.numel()
+        if isinstance(pending, PairSum):
+            if self.cast_first or self.one_plus:
+                x.add_(pending.a.float() + pending.b.float())
+                pending = None
+            else:
+                return self.add_norm_pair(x, pending, None, rows=rows)[0]
         if isinstance(pending, PostNormed):              # x += value / rms(value) * its weight (+ a row), then this norm
             if self.cast_first or self.one_plus or pending.eps != self.eps or \
                     (pending.weight is not None and pending.weight.dtype != self.weight.dtype):
