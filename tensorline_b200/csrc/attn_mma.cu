@@ -89,7 +89,14 @@ struct AttnArgs {
     TlTrace trace;
     bf16* k_pages_w; bf16* v_pages_w;
     const float* sink;                 // [nq] or null: one more term exp(sink[h]) in every softmax denominator of head h
+    int keep_first;                    // with a window: the keys at positions below it stay visible beside the window
 };
+
+// A window with kept first keys reads two runs of keys: [0, keep) and [lo, pos].  The kernels walk tiles of BN keys, so they
+// see the runs as one run of *virtual* positions: the tiles that hold kept keys and lie in front of the window's first tile
+// (k0 keys in all), then the tiles from the window's first one on (`base`, a multiple of BN).  k0 = 0 without kept keys.
+__device__ __forceinline__ int tl_kept_span(int keep, int base, int bn) { return min(base, ((keep + bn - 1) / bn) * bn); }
+__device__ __forceinline__ int tl_key_of(int v, int k0, int base) { return v < k0 ? v : v - k0 + base; }
 
 // Eight values at i0.. and the eight at D/2 + i0.. of one head's row: + bias, rotated (rotate-half pairs, angle of pair i in
 // cs[i] = cos, cs[D/2 + i] = sin) unless `rotate` is false, rounded to bfloat16.  The arithmetic of rope_kv_vec_kernel.
@@ -238,7 +245,7 @@ __device__ __forceinline__ float fast_exp2(float x) {          // 2^x, hardware 
 template <int NB, bool MASKED>
 __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
                                              const int (&pos_r)[2], const int (&lo_r)[2], int key0, float scale_log2,
-                                             int lane) {
+                                             int lane, int keep = 0) {
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
@@ -247,7 +254,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8
             const int r = e >> 1;
             if (MASKED) {
                 const int j = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
-                if (!(j <= pos_r[r] && j >= lo_r[r])) s[nb][e] = -INFINITY;
+                if (!(j <= pos_r[r] && (j >= lo_r[r] || j < keep))) s[nb][e] = -INFINITY;
             }
             mx[r] = fmaxf(mx[r], s[nb][e]);
         }
@@ -316,6 +323,11 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     const int pos_first = sp + row0 / g;
     const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
     const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN;
+    // the tiles this block walks: those that hold kept first keys in front of the window's first tile, then kt_lo .. kt_hi
+    const int keep = A.window > 0 ? A.keep_first : 0;
+    const int n_keep = min(kt_lo, (keep + BN - 1) / BN);
+    const int n_tiles = n_keep + kt_hi - kt_lo + 1;
+    const int kt_first = n_keep > 0 ? 0 : kt_lo;
 
     for (int idx = tid; idx < BM * CH; idx += 128) {       // Q tile: row = (token, head of the group)
         const int r = idx / CH, c = idx - r * CH;
@@ -331,8 +343,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     const int ppt = BN / A.page_size;                       // pages per tile
     const bf16* kbase = A.k_pages + (size_t)kh * A.page_size * D;
     const bf16* vbase = A.v_pages + (size_t)kh * A.page_size * D;
-    load_kv_tile(sK, kbase, tab + kt_lo * ppt, page_stride, kt_lo * BN, pos_hi, map, A.lim, TL_K_PREFILL);
-    load_kv_tile(sV, vbase, tab + kt_lo * ppt, page_stride, kt_lo * BN, pos_hi, map, A.lim, TL_K_PREFILL);
+    load_kv_tile(sK, kbase, tab + kt_first * ppt, page_stride, kt_first * BN, pos_hi, map, A.lim, TL_K_PREFILL);
+    load_kv_tile(sV, vbase, tab + kt_first * ppt, page_stride, kt_first * BN, pos_hi, map, A.lim, TL_K_PREFILL);
     cp_async_commit();
 
     int pos_r[2], lo_r[2];
@@ -352,17 +364,19 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     for (int nb = 0; nb < D / 8; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    for (int kt = kt_lo; kt <= kt_hi; ++kt) {
-        const int buf = (kt - kt_lo) & 1;
+    for (int it = 0; it < n_tiles; ++it) {
+        const int kt = it < n_keep ? it : kt_lo + (it - n_keep);
+        const int buf = it & 1;
         cp_async_wait<0>();
-        __syncthreads();                                   // tile kt is in; everyone is done with tile kt-1
-        if (kt < kt_hi) {
-            load_kv_tile(sK + (buf ^ 1) * BN * DP, kbase, tab + (kt + 1) * ppt, page_stride, (kt + 1) * BN, pos_hi, map, A.lim, TL_K_PREFILL);
-            load_kv_tile(sV + (buf ^ 1) * BN * DP, vbase, tab + (kt + 1) * ppt, page_stride, (kt + 1) * BN, pos_hi, map, A.lim, TL_K_PREFILL);
+        __syncthreads();                                   // tile kt is in; everyone is done with the tile before
+        if (it + 1 < n_tiles) {
+            const int nx = it + 1 < n_keep ? it + 1 : kt_lo + (it + 1 - n_keep);
+            load_kv_tile(sK + (buf ^ 1) * BN * DP, kbase, tab + nx * ppt, page_stride, nx * BN, pos_hi, map, A.lim, TL_K_PREFILL);
+            load_kv_tile(sV + (buf ^ 1) * BN * DP, vbase, tab + nx * ppt, page_stride, nx * BN, pos_hi, map, A.lim, TL_K_PREFILL);
         }
         cp_async_commit();
-        // skip tiles wholly outside this warp's rows (above the diagonal or behind the window)
-        if (!w_valid || kt * BN > w_pos_hi || kt * BN + BN - 1 < w_lo) continue;
+        // skip tiles wholly outside this warp's rows (above the diagonal, or behind the window and without a kept key)
+        if (!w_valid || kt * BN > w_pos_hi || (kt * BN + BN - 1 < w_lo && kt * BN >= keep)) continue;
         float s[BN / 8][4];
 #pragma unroll
         for (int nb = 0; nb < BN / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
@@ -370,9 +384,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
         // the tile's keys are all visible to all rows of the warp: below every row's position, inside
         // every row's window
         const bool full = (kt * BN + BN - 1 <= sp + wr_first / g) &&
-                          (A.window <= 0 || kt * BN >= max(0, w_pos_hi - A.window + 1));
+                          (A.window <= 0 || kt * BN >= max(0, w_pos_hi - A.window + 1) || kt * BN + BN <= keep);
         if (full) softmax_step<BN / 8, false>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane);
-        else      softmax_step<BN / 8, true>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane);
+        else      softmax_step<BN / 8, true>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane, keep);
         pv_tile<BN / 8>(o, s, sV + buf * BN * DP, 0, lane);
     }
     cp_async_wait<0>();
@@ -416,18 +430,22 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
     const int pos = A.start_pos[b], len = pos + 1;
     const int lo = A.window > 0 ? max(0, len - A.window) : 0;
     const int base = (lo / BN) * BN;
-    const int k_begin = base + split * A.chunk;
-    if (k_begin >= len) return;                            // an empty split: the combine step skips it too
-    const int k_end = min(len, k_begin + A.chunk);
-    const int n_stage = (k_end - k_begin + BN - 1) / BN;
+    // the request's keys as a run of virtual positions (see tl_kept_span); a block takes `chunk` of them
+    const int keep = A.window > 0 ? A.keep_first : 0;
+    const int k0 = tl_kept_span(keep, base, BN), vlen = k0 + len - base;
+    const int v_begin = split * A.chunk;
+    if (v_begin >= vlen) return;                           // an empty split: the combine step skips it too
+    const int v_end = min(vlen, v_begin + A.chunk);
+    const int n_stage = (v_end - v_begin + BN - 1) / BN;
     const int* gtab = A.table + (size_t)tl_checked(A.slots[b], A.lim.table_rows, A.lim, TL_K_DECODE) * A.max_pages;
     const int qrow = A.q_start[b];
-    // this block's part of the request's block table, copied once
+    // this block's part of the request's block table, copied once: the pages of every stage's tile
     int* stab = reinterpret_cast<int*>(smem_raw + DECODE_TAB_OFFSET);
-    const int ppt = BN / A.page_size, first_page = k_begin / A.page_size;
-    const int n_pages = (k_end - 1) / A.page_size - first_page + 1;
-    for (int i = tid; i < n_stage * ppt; i += 128)
-        stab[i] = i < n_pages ? gtab[tl_checked(first_page + i, A.max_pages, A.lim, TL_K_DECODE)] : 0;
+    const int ppt = BN / A.page_size, last_page = (len - 1) / A.page_size;
+    for (int i = tid; i < n_stage * ppt; i += 128) {
+        const int page = tl_key_of(v_begin + (i / ppt) * BN, k0, base) / A.page_size + i % ppt;
+        stab[i] = page <= last_page ? gtab[tl_checked(page, A.max_pages, A.lim, TL_K_DECODE)] : 0;
+    }
     TileMap<BN> map;
     map.init(tid, A.page_size);
     const size_t page_stride = (size_t)A.nkv * A.page_size * D;
@@ -451,8 +469,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
 #pragma unroll
     for (int st = 0; st < DEC_STAGES - 1; ++st) {
         if (st < n_stage) {
-            load_kv_tile(sK + st * BN * DP, kbase, stab + st * ppt, page_stride, k_begin + st * BN, k_end - 1, map, A.lim, TL_K_DECODE);
-            load_kv_tile(sV + st * BN * DP, vbase, stab + st * ppt, page_stride, k_begin + st * BN, k_end - 1, map, A.lim, TL_K_DECODE);
+            const int key_st = tl_key_of(v_begin + st * BN, k0, base);
+            load_kv_tile(sK + st * BN * DP, kbase, stab + st * ppt, page_stride, key_st, len - 1, map, A.lim, TL_K_DECODE);
+            load_kv_tile(sV + st * BN * DP, vbase, stab + st * ppt, page_stride, key_st, len - 1, map, A.lim, TL_K_DECODE);
         }
         cp_async_commit();
     }
@@ -462,8 +481,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
 #pragma unroll
     for (int kb = 0; kb < KBLK; ++kb)
         ldsm_x4(qf[kb], sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + kb * 16 + (lane >> 4) * 8);
-    const int pos_r[2] = {k_end - 1, k_end - 1};           // every row sees all keys of the range
-    const int lo_r[2] = {max(lo, k_begin), max(lo, k_begin)};
+    const int pos_r[2] = {len - 1, len - 1};               // every row sees the request's keys up to its own
+    const int lo_r[2] = {lo, lo};
     float o[D / 8][4];
 #pragma unroll
     for (int nb = 0; nb < D / 8; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
@@ -474,19 +493,20 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
         __syncthreads();
         if (st + DEC_STAGES - 1 < n_stage) {
             const int nst = st + DEC_STAGES - 1, nb_ = nst % DEC_STAGES;
-            load_kv_tile(sK + nb_ * BN * DP, kbase, stab + nst * ppt, page_stride, k_begin + nst * BN, k_end - 1, map, A.lim, TL_K_DECODE);
-            load_kv_tile(sV + nb_ * BN * DP, vbase, stab + nst * ppt, page_stride, k_begin + nst * BN, k_end - 1, map, A.lim, TL_K_DECODE);
+            const int key_st = tl_key_of(v_begin + nst * BN, k0, base);
+            load_kv_tile(sK + nb_ * BN * DP, kbase, stab + nst * ppt, page_stride, key_st, len - 1, map, A.lim, TL_K_DECODE);
+            load_kv_tile(sV + nb_ * BN * DP, vbase, stab + nst * ppt, page_stride, key_st, len - 1, map, A.lim, TL_K_DECODE);
         }
         cp_async_commit();
         const int buf = st % DEC_STAGES;
-        const int key0 = k_begin + st * BN + warp * 16;    // this warp's 16 keys of the stage
-        if (key0 >= k_end) continue;
+        const int key0 = tl_key_of(v_begin + st * BN, k0, base) + warp * 16;    // this warp's 16 keys of the stage
+        if (key0 >= len) continue;
         float s[2][4];
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
         qk_tile_regs<2>(s, qf, sK + buf * BN * DP, warp * 16, lane);
-        if (key0 + 16 <= k_end && key0 >= lo) softmax_step<2, false>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
-        else                                  softmax_step<2, true>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
+        if (key0 + 16 <= len && (key0 >= lo || key0 + 16 <= keep)) softmax_step<2, false>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
+        else softmax_step<2, true>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane, keep);
         pv_tile<2>(o, s, sV + buf * BN * DP, warp * 16, lane);
     }
     cp_async_wait<0>();
@@ -936,7 +956,8 @@ __global__ void attn_combine_kernel(const AttnArgs A) {
     const int len = A.start_pos[b] + 1;
     const int lo = A.window > 0 ? max(0, len - A.window) : 0;
     const int base = (lo / BN) * BN;
-    const int ns = min(A.splits, (len - base + A.chunk - 1) / A.chunk);
+    const int vlen = tl_kept_span(A.window > 0 ? A.keep_first : 0, base, BN) + len - base;
+    const int ns = min(A.splits, (vlen + A.chunk - 1) / A.chunk);
     const size_t p0 = ((size_t)b * A.nq + head) * A.splits;
     __shared__ float wgt[128];                             // a split's weight exp2(m_s - m); at most 128 splits
     __shared__ float inv_total;
@@ -1025,6 +1046,10 @@ TL_EXPORT int tl_attn_head_dim() { return D; }
 // launchers set it before every launch, so the entry points keep their arguments.
 static const float* g_sink = nullptr;
 TL_EXPORT int tl_attn_set_sink(const float* sink) { g_sink = sink; return 0; }
+// The kept first keys of the launches that follow (with a window: positions below it stay visible); 0: none.  The mma.sync
+// prompt kernel and the cp.async decode kernel read them; the TMA decode kernel turns such a launch down (code 2).
+static int g_keep_first = 0;
+TL_EXPORT int tl_attn_set_keep_first(int keep_first) { g_keep_first = keep_first > 0 ? keep_first : 0; return 0; }
 // 1 if this library was compiled as the checking build (-DTL_CHECK=1).
 TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 // Block-table entries a decode block may copy: chunk / page_size of a decode call may not exceed it.
@@ -1047,6 +1072,7 @@ TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.order = order;
+    A.keep_first = g_keep_first;
     A.lim = TlLimits{table_rows, total_pages, fault};
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
@@ -1076,6 +1102,7 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
     A.chunk = chunk; A.splits = splits; A.part_o = part_o; A.part_ml = part_ml;
+    A.keep_first = g_keep_first;
     A.lim = TlLimits{table_rows, total_pages, fault};
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
@@ -1124,6 +1151,7 @@ int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages,
                     int* status, int cluster_merge, int table_rows, int* fault, const RopeFold& R, cudaStream_t stream) {
 #if HEAD_DIM % 64 == 0
     if (B <= 0) return 0;
+    if (g_keep_first > 0 && window > 0) return 2;          // two runs of keys: the cp.async kernel walks them
     if (R.inv_freq && ((q_stride & 7) || ((uintptr_t)q & 15) || (R.bias && ((uintptr_t)R.bias & 15)))) return 2;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
     // cluster_merge: the key ranges of a (request, KV head) merge inside a thread-block cluster, no partials needed

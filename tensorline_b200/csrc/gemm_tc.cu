@@ -108,9 +108,9 @@ __device__ __forceinline__ const float* cluster_peer(const float* p, int rank) {
 }
 
 // silu(gate) * up of two accumulator values, each rounded to bfloat16 first (as a stored gate|up product would have been).
-// `kind`: 1 silu, 2 the tanh form of gelu.
-__device__ __forceinline__ float silu_mul_rounded(float gate, float up, int kind) {
-    return tl_gate_mul(__bfloat162float(__float2bfloat16_rn(gate)), __bfloat162float(__float2bfloat16_rn(up)), kind);
+// `kind`: 1 silu, 2 the tanh form of gelu, 3 the clamped swish with its constants `limit` and `alpha`.
+__device__ __forceinline__ float silu_mul_rounded(float gate, float up, int kind, float limit, float alpha) {
+    return tl_gate_mul(__bfloat162float(__float2bfloat16_rn(gate)), __bfloat162float(__float2bfloat16_rn(up)), kind, limit, alpha);
 }
 
 struct GemmArgs {
@@ -127,6 +127,7 @@ struct GemmArgs {
                           // distributed shared memory: no pieces in global memory (swap = 1, 2..8 ranges)
     int gated;            // swap, one split: rows 0..63 of every 128-row tile of A are gate features, rows 64..127 the
                           // up features of the same 64 columns; out[b, 64 tile + j] = silu(gate) * up, [RB, RA / 2]
+    float gate_limit, gate_alpha;   // gated = 3: the clamped swish's constants
     long long wait_cycles;   // how long a wait on a barrier may take before the block gives up
     int drop_last_load;      // tests only: the copy thread leaves out its last stage, so the MMA thread's wait runs out
     // The residual add folded into the product that makes the addend (swap, cluster_reduce): the block that finishes a
@@ -403,7 +404,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int j = 0; j < 8; ++j) {
                         const int t = up_side ? 8 + j : j;
                         const float mine = __uint_as_float(up_side ? r[8 + j] : r[j]), other = hand[t * 64 + f];
-                        res[j] = silu_mul_rounded(up_side ? other : mine, up_side ? mine : other, G.gated);
+                        res[j] = silu_mul_rounded(up_side ? other : mine, up_side ? mine : other, G.gated, G.gate_limit, G.gate_alpha);
                     }
                     if (col < (G.RA >> 1)) {
                         bf16* dst = (bf16*)G.out + (size_t)(b0 + c0 + (up_side ? 8 : 0)) * G.ldo + col;
@@ -683,6 +684,11 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& G, dim3
 
 }  // namespace
 
+// The constants of the clamped swish (gated = 3) for the launches that follow: with g' = min(g, limit) and
+// u' = clamp(u, -limit, limit) the epilogue writes g' sigmoid(alpha g') (u' + 1).  Set before every such launch.
+static float g_gate_limit = 0.f, g_gate_alpha = 1.f;
+TL_EXPORT int tl_gemm_tc_set_gate(float limit, float alpha) { g_gate_limit = limit; g_gate_alpha = alpha; return 0; }
+
 // y[T, N] = x[T, K] w[N, K]^T.  swap = 1 puts w on the 128-row side (few tokens), swap = 0 puts x there.
 // bn: columns of the other side per tile (16, 32, 64, 128 or 256).  splits > 1 needs `partial`
 // (splits * T * N floats); with `counters` (n_counters zeroed ints, at least one per tile, left zeroed) the
@@ -724,6 +730,7 @@ int gemm_impl(const void* x, const void* w, void* y, int out_f32, int ldo, int T
     if (gated && (!swap || splits != 1 || out_f32 || (N & 127) || y == nullptr)) return 1;   // whole 64 + 64 tiles, one split
     GemmArgs G{};
     G.gated = gated;
+    G.gate_limit = g_gate_limit; G.gate_alpha = g_gate_alpha;
     G.cluster_reduce = (cluster_reduce && splits >= 2) ? 1 : 0;
     if (cluster_reduce && (!swap || splits > 8 || (y == nullptr && !adds))) return 1;
     if (adds && !G.cluster_reduce) return 1;                                             // the caller's plan must give 2..8 ranges

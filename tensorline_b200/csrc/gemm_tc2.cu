@@ -121,8 +121,14 @@ struct Gemm2Args {
     int T, N, K;
     int m_tiles, n_tiles;  // tiles of 256 rows and 256 columns
     int out_f32, gated;
+    float gate_limit, gate_alpha;   // gated = 3: the clamped swish's constants
     int* status;
 };
+
+// The constants of the clamped swish (gated = 3) for the launches that follow: with g' = min(g, limit) and
+// u' = clamp(u, -limit, limit) the epilogue writes g' sigmoid(alpha g') (u' + 1).  Set before every such launch.
+static float g_gate_limit = 0.f, g_gate_alpha = 1.f;
+TL_EXPORT int tl_gemm_tc2_set_gate(float limit, float alpha) { g_gate_limit = limit; g_gate_alpha = alpha; return 0; }
 
 __device__ __forceinline__ void store16_bf16(bf16* dst, const float (&v)[16], int valid) {
     if (valid >= 16 && ((((uintptr_t)dst) & 15) == 0)) {
@@ -249,7 +255,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                             for (int j = 0; j < 16; ++j) {
                                 const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(rg[j])));
                                 const float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(ru[j])));
-                                v[j] = tl_gate_mul(g, u, G.gated);
+                                v[j] = tl_gate_mul(g, u, G.gated, G.gate_limit, G.gate_alpha);
                             }
                             store16_bf16((bf16*)G.out + (size_t)t * G.ldo + col, v, (G.N >> 1) - col);
                         }
@@ -375,6 +381,7 @@ TL_EXPORT int tl_gemm_tc2(const void* x, const void* w, void* y, int out_f32, in
     G.out = y; G.ldo = ldo; G.T = T; G.N = N; G.K = K;
     G.m_tiles = (T + 2 * BM - 1) / (2 * BM); G.n_tiles = (N + BN - 1) / BN;
     G.out_f32 = out_f32; G.gated = gated; G.status = status;
+    G.gate_limit = g_gate_limit; G.gate_alpha = g_gate_alpha;
     long long tiles = (long long)G.m_tiles * G.n_tiles;
     int pairs = tl_num_sms() / 2;
     if (max_pairs > 0 && max_pairs < pairs) pairs = max_pairs;

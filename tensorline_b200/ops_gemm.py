@@ -34,6 +34,8 @@ def lib():
                                         _P, _I, _P, _P, _P, _I, _P, _I, ctypes.c_float, _P]
         l.tl_gemm_tc_normed.restype = ctypes.c_int
         l.tl_splitk_reduce.argtypes = [_P, _P, _I, _I, _I, _I, _I, _P]
+        l.tl_gemm_tc_set_gate.argtypes = [ctypes.c_float, ctypes.c_float]
+        l.tl_gemm_tc_set_gate.restype = ctypes.c_int
         l.tl_splitk_reduce.restype = ctypes.c_int
         _lib = l
     return _lib
@@ -149,6 +151,8 @@ def gemm_tc(x, w: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16, *, swap
             + ("" if swap else "+rows") + ("+normed" if normed is not None else "") + ("+residual" if residual is not None else ""))
     launches = 1 if (splits == 1 or fused_reduce or pieces or use_cluster) else 2
     counters = (st.data_ptr() + 4) if fused_reduce else None
+    if isinstance(gated, tuple):
+        lib().tl_gemm_tc_set_gate(float(gated[1]), float(gated[2]))
     if normed is None and residual is None:
         _check(lib().tl_gemm_tc(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), ldo, T, N, K, swap, bn, splits,
                                 _ptr(partial), _ptr(st), counters, N_COUNTERS, _gate_code(gated), int(use_cluster), _stream()),
@@ -176,6 +180,8 @@ def lib2():
         l = load_library("tl_gemm_tc2", ["gemm_tc2.cu"])
         l.tl_gemm_tc2.argtypes = [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _I, _P]
         l.tl_gemm_tc2.restype = ctypes.c_int
+        l.tl_gemm_tc2_set_gate.argtypes = [ctypes.c_float, ctypes.c_float]
+        l.tl_gemm_tc2_set_gate.restype = ctypes.c_int
         _lib2 = l
     return _lib2
 
@@ -203,20 +209,25 @@ def gemm_tc2(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype = torch.bf
     elif out.shape != (T, cols) or out.dtype != out_dtype or out.stride(1) != 1:
         raise KernelError("gemm_tc2: out must be [T, N] (gated: [T, N / 2]) of the output type with unit inner stride")
     st = status_word(x.device)
+    if isinstance(gated, tuple):
+        lib2().tl_gemm_tc2_set_gate(float(gated[1]), float(gated[2]))
     _check(lib2().tl_gemm_tc2(_ptr(x), _ptr(w), _ptr(out), int(out_dtype == torch.float32), out.stride(0), T, N, K,
                               _gate_code(gated), _ptr(st), int(max_pairs), _stream()), "gemm_tc2" + ("+gated" if gated else ""))
     return out
 
 
 def _gate_code(gated) -> int:
-    """`gated` False / True ("silu") / "gelu_tanh" as the kernels take it: 0, 1, 2."""
+    """`gated` False / True ("silu") / "gelu_tanh" / ("swish_clamped", limit, alpha) as the kernels take it: 0, 1, 2, 3 (the
+    constants of the last travel through the library's `set_gate`)."""
     if not gated:
         return 0
+    if isinstance(gated, tuple) and len(gated) == 3 and gated[0] == "swish_clamped" and gated[1] > 0:
+        return 3
     if gated is True or gated == "silu":
         return 1
     if gated == "gelu_tanh":
         return 2
-    raise KernelError(f"a gated epilogue applies 'silu' or 'gelu_tanh', not {gated!r}")
+    raise KernelError(f"a gated epilogue applies 'silu', 'gelu_tanh' or ('swish_clamped', limit, alpha), not {gated!r}")
 
 
 def can_gate(T: int, N: int, K: int) -> bool:
