@@ -585,10 +585,30 @@ def _dekerax_sizes(z):
             "layers": [order[i % 4] for i in range(z["layers"])]}
 
 
+def _sumuvik_sizes(z):
+    """Four layers: the gated linear recurrence, attention over a window of 1,024 keys beside 128 kept first ones, the same over
+    2,048 keys, the recurrence; one dense feed-forward, three routed ones (four groups of experts, two kept) with a shared
+    expert.  The recurrence is as wide as the delta rule's values at the same size, its gates' blocks as wide as one of its heads."""
+    moe = {"expert": {"ff": z["ff"], "limit": 7.0}, "kind": "moe", "shared": {"ff": z["ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "groups": {"count": 4, "keep": 2}, "scale": 2.5, "top": z["top"]}}
+    rec = {"type": "rglru", "mlp": moe, "mixer": {"width": z["rec_heads"] * z["rec_vdim"], "blocks": z["rec_heads"], "conv": 4}}
+
+    def attention(window, mlp):
+        return {"type": "attention", "mlp": mlp, "mixer": {
+            "heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head"], "vdim": z["head"], "scale": z["head"] ** -0.5,
+            "mask": {"size": window, "keep_first": 128},
+            "rot": {"base": 500000.0, "dims": z["head"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    dense = {"kind": "dense", "ff": 2 * z["top"] * z["ff"] // 3 // 64 * 64, "limit": 7.0}
+    order = [rec, attention(1024, dense), attention(2048, moe), rec]
+    return {"architecture": "Sumuvik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [order[i % 4] for i in range(z["layers"])]}
+
+
 def run_design(a):
     import torch
     from tensorline_b200 import Engine, Qwen2Config
     from tensorline_b200.config.dekerax import DekeraxConfig
+    from tensorline_b200.config.sumuvik import SumuvikConfig
     from tensorline_b200.config.vutesun import VutesunConfig
     if not torch.cuda.is_available():
         print(json.dumps({"impl": "ours", "error": "no CUDA device: this engine runs on the GPU only"}))
@@ -606,6 +626,8 @@ def run_design(a):
                                                     vocab_size=z["vocab"], eos_token_id=None))}
         if a.design == "dekerax":                                        # beside the closest design the engine has, at equal sizes
             arms = {"dekerax": DekeraxConfig.from_dict(_dekerax_sizes(z)), "vutesun": arms["vutesun"]}
+        if a.design == "sumuvik":                                        # its closest: windows, a recurrence behind a convolution, a shared expert
+            arms = {"sumuvik": SumuvikConfig.from_dict(_sumuvik_sizes(z)), "dekerax": DekeraxConfig.from_dict(_dekerax_sizes(z))}
         out[tag] = {"sizes": dict(z, dense_intermediate=dense)}
         for name, cfg in arms.items():
             weights = random_weights(cfg, device)
@@ -629,7 +651,7 @@ def run_design(a):
             import gc
             gc.collect(); torch.cuda.empty_cache()
     first = out[sorted(out)[0]]
-    beside = {"vutesun": "Qwen2", "dekerax": "Vutesun"}[a.design]
+    beside = {"vutesun": "Qwen2", "dekerax": "Vutesun", "sumuvik": "Dekerax"}[a.design]
     print(json.dumps({"metric": f"decode tok/s of the {a.design.capitalize()} decoder beside {beside} at equal layer sizes (bf16, batch {batch}, context {context})",
                       "value": first[a.design][f"decode_b{batch}_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
                       "ms_per_step": first[a.design][f"decode_b{batch}_ms"], "higher_is_better": True, "scaling": "weak",
@@ -668,9 +690,9 @@ def main(argv=None):
     ap.add_argument("--timeline", action="store_true",
                     help="print the time line of one captured decode step from the kernels' own stamps (needs TENSORLINE_B200_TRACE=1)")
     ap.add_argument("--no-warm-mix", dest="warm_mix", action="store_false", help="mix: time the first pass (graph capture included)")
-    ap.add_argument("--design", choices=["vutesun", "dekerax"], default=None,
+    ap.add_argument("--design", choices=["vutesun", "dekerax", "sumuvik"], default=None,
                     help="instead of the default workload: this design beside the closest other one at equal layer sizes "
-                         "(vutesun beside Qwen2, dekerax beside vutesun; prefill, decode, --profile)")
+                         "(vutesun beside Qwen2, dekerax beside vutesun, sumuvik beside dekerax; prefill, decode, --profile)")
     ap.add_argument("--design-size", default="", help="--design: which of the sizes (2k, 4k; commas between them; default all)")
     a = ap.parse_args(argv)
     if a.warmup < 3:
