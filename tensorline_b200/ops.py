@@ -42,7 +42,9 @@ _SIGNATURES = {
     "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _F, _P],
     "tl_route_groups": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P],
     "tl_causal_conv": [_P, _I, _I, _P, _P, _P, _I, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _P],
-    "tl_rglru_scan": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "tl_rglru_scan": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, ctypes.c_longlong, _P],
+    "tl_split3": [_P, _P, _I, _I, _I, _P],
+    "tl_rglru_chunk": [],
     "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
     "tl_moe_sort": [_P, _I, _I, _P, _P, _P, _P],
     "tl_moe_gather": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P],
@@ -913,14 +915,21 @@ def causal_conv(proj: torch.Tensor, off: int, in_bias: torch.Tensor | None, W: i
 
 def rglru_scan(gates: torch.Tensor, gate_bias: torch.Tensor, u: torch.Tensor, proj: torch.Tensor, in_bias: torch.Tensor | None,
                lam: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, *, B: int,
-               blocks: int, sharpness: float, max_q_len: int, y_off: int = 0) -> None:
+               blocks: int, sharpness: float, max_q_len: int, y_off: int = 0, in_order: bool = False, by_block: bool = False) -> None:
     """Per (request, channel c), tokens in order, from the state in `state[slot]` (float32 [W], left up to date):
     r = sigmoid(zr + br), i = sigmoid(zi + bi), log a = -sharpness r softplus(lam[c]), S <- exp(log a) S + sqrt(1 - a^2) i u[t, c],
     out[t, c] = S gelu_tanh(proj[t, y_off + c] + in_bias[y_off + c]).  gates float32 [T, 2W]: for each of the `blocks` equal
-    parts of the channels its r pre-activations, then its i pre-activations; gate_bias float32 laid out alike."""
+    parts of the channels its r pre-activations, then its i pre-activations (with `by_block`: [blocks, T, 2W / blocks], what a
+    batched product leaves); gate_bias float32 [2W] laid out as a row of the former.
+    A step with a request of two chunks of tokens or more (`rglru_chunk()`) runs its chunks side by side: per chunk the
+    product of its decays and the state it reaches from zero, the chunks' starting states from these in order, then every
+    chunk's tokens from its starting state.  A chunk's starting state is summed in another order than token by token, so it
+    differs by roundings of float; `in_order` keeps every step in the one order (the float32 engine, whose results do not
+    depend on how a prompt was cut, asks for it)."""
     T, W = u.shape
-    if gates.shape != (T, 2 * W) or gates.dtype != torch.float32 or u.dtype != torch.float32 or out.shape != (T, W):
-        raise KernelError("rglru_scan: gates float32 [T, 2W], u float32 [T, W], out [T, W]")
+    if gates.numel() != 2 * T * W or gates.dtype != torch.float32 or u.dtype != torch.float32 or out.shape != (T, W) or W % blocks or \
+            gates.shape != ((blocks, T, 2 * W // blocks) if by_block else (T, 2 * W)):
+        raise KernelError("rglru_scan: gates float32 [T, 2W] or [blocks, T, 2W / blocks], u float32 [T, W], out [T, W]")
     if proj.dtype != torch.float32 or proj.stride(1) != 1 or proj.shape[1] < y_off + W or proj.shape[0] != T:
         raise KernelError("rglru_scan: proj float32 [T, >= y_off + W]")
     if W % blocks or gate_bias.numel() != 2 * W or gate_bias.dtype != torch.float32 or lam.numel() != W or lam.dtype != torch.float32:
@@ -931,6 +940,35 @@ def rglru_scan(gates: torch.Tensor, gate_bias: torch.Tensor, u: torch.Tensor, pr
         raise KernelError("rglru_scan: a slot holds W floats")
     _contig(gates, "gates"); _contig(gate_bias, "gate_bias"); _contig(u, "u"); _contig(lam, "lam"); _contig(state, "state")
     _contig(out, "out"); _ints(q_start, "q_start"); _ints(slots, "slots")
+    summary, chunks, bw = None, 0, W // blocks
+    if not in_order and max_q_len >= 2 * rglru_chunk():
+        chunks = -(-int(max_q_len) // rglru_chunk())
+        summary = torch.empty((int(B), chunks, 2, W), dtype=torch.float32, device=u.device)
     _check(core().tl_rglru_scan(_ptr(gates), _ptr(gate_bias), _ptr(u), _ptr(proj), proj.stride(0), int(y_off), _ptr(in_bias), _ptr(lam),
                                 _ptr(state), _ptr(q_start), _ptr(slots), _ptr(out), dtype_code(out.dtype), int(B), W, int(blocks),
-                                float(sharpness), int(max_q_len), _stream()), "rglru_scan")
+                                float(sharpness), int(max_q_len), _ptr(summary), chunks, T * 2 * bw if by_block else 2 * bw,
+                                2 * bw if by_block else 2 * W, _stream()), "rglru_scan")
+
+
+def split3(x: torch.Tensor, blocks: int) -> torch.Tensor:
+    """A float32 [T, W] as bfloat16 [blocks, T, 3 * (W / blocks)]: per block of channels the leading, the middle and the last
+    part of every float, three bfloat16 numbers that sum to it to within one part in 2^24.  Its batched product with
+    bfloat16 weights stacked three times, summed in float32 on the tensor cores, is as exact as a float32 product."""
+    T, W = x.shape
+    if x.dtype != torch.float32 or W % blocks:
+        raise KernelError("split3: float32 [T, W], W a multiple of blocks")
+    _contig(x, "x")
+    parts = torch.empty((blocks, T, 3 * (W // blocks)), dtype=torch.bfloat16, device=x.device)
+    _check(core().tl_split3(_ptr(x), _ptr(parts), T, W, int(blocks), _stream()), "split3")
+    return parts
+
+
+_RGLRU_CHUNK = None
+
+
+def rglru_chunk() -> int:
+    """Tokens of one chunk of a long step of `rglru_scan`."""
+    global _RGLRU_CHUNK
+    if _RGLRU_CHUNK is None:
+        _RGLRU_CHUNK = int(core().tl_rglru_chunk())
+    return _RGLRU_CHUNK

@@ -12,7 +12,9 @@ Local Attention for Efficient Language Models").
 
 Between steps a request keeps, in its state slots, S (float32 [width]) and the convolution's last `taps - 1` inputs
 (float32); both start at zero.  Everything behind the two projections is float32 in both engines: the projections'
-float32 accumulators are kept as they are, the gates' products, the decay and the state never leave float32.  The mixer
+float32 accumulators are kept as they are, the gates' products, the decay and the state never leave float32.  The bfloat16
+engine runs a long step's recurrence as chunks side by side (`ops.rglru_scan`); the float32 engine walks every step in
+order, so that its results are the same floats however a prompt was cut.  The mixer
 reads the step from device tensors only (single-token steps sit in CUDA graphs).
 """
 from __future__ import annotations
@@ -23,6 +25,11 @@ from .. import ops
 from ..cache import SlotState
 from .base import Part, Runtime, TensorSpec, register_mixer
 from .linear import matmul, resolve
+
+# From this many tokens a bfloat16 step takes the gates' products, which are float32 products of a float32 input, as one
+# batched library product on the tensor cores (the engine's other long products are the library's too) of the input cut
+# into three bfloat16 parts; shorter steps and the float32 engine use the package's float32 kernel.
+GATE_PRODUCT_LIBRARY_MIN_TOKENS = 256
 
 _NAMES = {"y": "y", "y_bias": "y.b", "x": "x", "x_bias": "x.b", "conv": "conv", "conv_bias": "conv.b", "ra": "ra", "ra_bias": "ra.b",
           "ri": "ri", "ri_bias": "ri.b", "lam": "lam", "o": "o"}
@@ -42,7 +49,7 @@ class RGLRU(Part):
         self.hidden, self.W, self.blocks, self.taps, self.sharpness = hidden, width, blocks, taps, float(sharpness)
         self.bw = width // blocks
         self.names = {**_NAMES, **(names or {})}
-        self.w_in = self.b_in = self.conv_w = self.conv_b = self.w_gates = self.b_gates = self.lam = self.w_o = None
+        self.w_in = self.b_in = self.conv_w = self.conv_b = self.w_gates = self.w_gates3 = self.b_gates = self.lam = self.w_o = None
 
     def cache_need(self):
         need = {"memory": SlotState((self.W,), "float32")}
@@ -68,6 +75,8 @@ class RGLRU(Part):
         self.conv_b = weights[n["conv_bias"]].float().contiguous()
         # the gates' matrices per block as [in, r outputs | i outputs], in their stored type (products and sums are float32)
         self.w_gates = torch.cat([weights[n["ra"]].transpose(1, 2), weights[n["ri"]].transpose(1, 2)], dim=2).contiguous()
+        # for long bfloat16 steps: the same three times over the input side, for the three parts of a float (`ops.split3`)
+        self.w_gates3 = self.w_gates.repeat(1, 3, 1).contiguous() if self.w_gates.dtype == torch.bfloat16 else None
         self.b_gates = torch.cat([weights[n["ra_bias"]], weights[n["ri_bias"]]], dim=1).float().contiguous()      # [blocks, 2 bw]
         self.lam = weights[n["lam"]].float().contiguous()
         self.w_o = self._compute_copy(weights[n["o"]])
@@ -81,9 +90,16 @@ class RGLRU(Part):
         inputs = cache["inputs"].state if self.taps > 1 else None
         ops.causal_conv(proj, W, self.b_in, W, self.conv_w, self.conv_b, inputs, ctx.q_start, ctx.slots, u, B=ctx.B,
                         max_q_len=ctx.max_q_len)
-        gates = torch.empty((T, 2 * W), dtype=torch.float32, device=h.device)    # per block: r pre-activations, then i
-        ops.head_matmul(u, self.w_gates, gates, nb, bw, 2 * bw, bw, 2 * bw)
+        by_block = h.dtype == torch.bfloat16 and T >= GATE_PRODUCT_LIBRARY_MIN_TOKENS and self.w_gates3 is not None and \
+            not ctx.graph_max_ctx
+        if by_block:                                     # one batched library product of the floats' three bfloat16 parts
+            gates = torch.bmm(ops.split3(u, nb), self.w_gates3, out_dtype=torch.float32)        # [blocks, T, 2 bw]
+            ops.mark("library product")
+        else:
+            gates = torch.empty((T, 2 * W), dtype=torch.float32, device=h.device)    # per block: r pre-activations, then i
+            ops.head_matmul(u, self.w_gates, gates, nb, bw, 2 * bw, bw, 2 * bw)
         out = torch.empty((T, W), dtype=h.dtype, device=h.device)
         ops.rglru_scan(gates, self.b_gates, u, proj, self.b_in, self.lam, cache["memory"].state, ctx.q_start, ctx.slots, out,
-                       B=ctx.B, blocks=nb, sharpness=self.sharpness, max_q_len=ctx.max_q_len)
+                       B=ctx.B, blocks=nb, sharpness=self.sharpness, max_q_len=ctx.max_q_len, in_order=h.dtype == torch.float32,
+                       by_block=by_block)
         return matmul(out, self.w_o, may_defer=True, to_residual=True)

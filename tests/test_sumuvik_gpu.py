@@ -344,7 +344,7 @@ def test_recurrence_in_one_step_and_in_portions(adt, W, nb):
     want, last = _scan_plain(gates.double(), gb.double(), u.double(), proj[:, 9:].double(), yb[9:].double(), lam.double(), nb, LENS)
     slots = [5, 0, 3, 1]
     results = []
-    for cuts in ([[1000] * 4], CUTS[1:]):
+    for cuts in ([[1000] * 4], CUTS[1:], [[7, 5, 13, 9]] * 13):
         state = torch.zeros(7, W, device="cuda")
         state[2] = 7.0
         got = torch.zeros(T, W)
@@ -361,7 +361,67 @@ def test_recurrence_in_one_step_and_in_portions(adt, W, nb):
             assert_close(state[slot], last[b], "the state a request keeps", **F32)
         assert float(state[2].min()) == 7.0
         results.append((got, state.cpu()))
-    assert torch.equal(results[0][1], results[1][1]), "the state after a token does not depend on how the tokens were cut"
+    assert torch.equal(results[1][1], results[2][1]), "the state after short steps does not depend on how the tokens were cut"
+
+
+@pytest.mark.parametrize("W,nb,T", [(40, 5, 300), (39, 3, 257), (512, 2, 64), (96, 1, 1)])
+def test_a_float_in_three_parts_and_the_gates_from_them(W, nb, T):
+    """Three bfloat16 parts sum to the float within one part in 2^24 (values of every size, zeros, tiny ones), and the batched
+    product of the parts with bfloat16 weights stacked three times is the float32 product."""
+    from tensorline_b200 import ops
+    bw = W // nb
+    x = rnd(T, W, seed=21) * torch.exp(rnd(T, W, seed=22) * 6.0)
+    x[0, :3] = torch.tensor([0.0, 1e-30, -3.0e38 / 1e4])
+    parts = ops.split3(x.cuda(), nb)
+    assert parts.shape == (nb, T, 3 * bw) and parts.dtype == torch.bfloat16
+    back = parts.double().cpu().view(nb, T, 3, bw).sum(2).permute(1, 0, 2).reshape(T, W)
+    assert float(((back - x.double()).abs() / x.double().abs().clamp_min(1e-30)).max()) <= 2.0 ** -23
+    w = rnd(nb, bw, 2 * bw, seed=23).to(torch.bfloat16)
+    got = torch.bmm(parts, w.cuda().repeat(1, 3, 1), out_dtype=torch.float32).cpu()
+    want = torch.einsum("tbk,bkn->btn", x.double().view(T, nb, bw), w.double())
+    scale = torch.einsum("tbk,bkn->btn", x.double().abs().view(T, nb, bw), w.double().abs())
+    assert float(((got.double() - want).abs() / scale.clamp_min(1e-30)).max()) < 4e-6
+
+
+@pytest.mark.parametrize("by_block", [False, True])
+@pytest.mark.parametrize("adt", DT)
+@pytest.mark.parametrize("W,nb", [(40, 5), (130, 2), (520, 4)])
+def test_recurrence_of_long_steps_in_chunks(adt, W, nb, by_block):
+    """Steps long enough to run as chunks side by side: requests that end one token before, at and one token after a chunk's
+    edge, a single token and a request of many chunks in one launch, then the same requests in portions whose edges fall
+    inside chunks, and continued token by token from the state the long step left."""
+    from tensorline_b200 import ops
+    C = ops.rglru_chunk()
+    lens = [2 * C - 1, 2 * C, 2 * C + 1, 1, 9 * C + 5, C]
+    T = sum(lens)
+    gates, gb = rnd(T, 2 * W, seed=11, scale=2.0), rnd(2 * W, seed=12)
+    u, proj, yb = rnd(T, W, seed=13), rnd(T, W, seed=14), rnd(W, seed=15)
+    lam = torch.rand(W, generator=torch.Generator().manual_seed(16)) * 6.0 - 8.0
+    want, last = _scan_plain(gates.double(), gb.double(), u.double(), proj.double(), yb.double(), lam.double(), nb, lens)
+    slots = [4, 6, 0, 2, 1, 5]
+    n = len(lens)
+    tail = [[0, 0, 0, 0, 1, 0]] * 6
+    for cuts in ([[10 ** 6] * n], [[2 * C + 1] * n, [3 * C - 2] * n, [10 ** 6] * n], [[5, 0, 0, 0, 9 * C - 1, 0], [10 ** 6] * n],
+                 [[10 ** 6, 10 ** 6, 10 ** 6, 10 ** 6, 9 * C - 1, 10 ** 6]] + tail):
+        state = torch.full((8, W), float("nan"), device="cuda")
+        state[slots] = 0.0
+        state[3] = 7.0
+        got = torch.zeros(T, W)
+
+        def step(rows, q_start, live):
+            out = torch.empty(len(rows), W, dtype=adt, device="cuda")
+            g = gates[rows].contiguous()
+            if by_block:                                               # as a batched product per block leaves them
+                g = g.view(len(rows), nb, 2 * (W // nb)).transpose(0, 1).contiguous()
+            ops.rglru_scan(g.cuda(), gb.cuda(), u[rows].contiguous().cuda(), proj[rows].contiguous().cuda(), yb.cuda(),
+                           lam.cuda(), state, i32(q_start), i32(live), out, B=len(live), blocks=nb, sharpness=8.0,
+                           max_q_len=max(b - a for a, b in zip(q_start, q_start[1:])), by_block=by_block)
+            got[rows] = out.float().cpu()
+        _run_in_cuts(lens, cuts, slots, step)
+        assert_close(got, want, f"recurrence in chunks, {len(cuts)} launches", **tol(adt))
+        for b, slot in enumerate(slots):
+            assert_close(state[slot], last[b], "the state a request keeps", **F32)
+        assert float(state[3].min()) == 7.0 and bool(torch.isnan(state[7]).all())
 
 
 @pytest.mark.parametrize("decoded", [0, 300])
@@ -490,6 +550,17 @@ def test_all_schedules_agree_with_the_plain_model(model, dtype):
         for what, got in results.items():
             for key, row in got.items():
                 assert torch.equal(row, results["whole"][key]), f"{what} differs from whole at {key}"
+
+
+def test_the_forms_of_long_steps_agree_with_the_plain_model(model, monkeypatch):
+    """The bfloat16 engine's forms for long steps (the gates from three parts of a float through a batched product, the
+    recurrence in chunks side by side) taken from two tokens on: whole prompts, changing portions and mixed batches."""
+    from tensorline_b200.parts import rglru
+    monkeypatch.setattr(rglru, "GATE_PRODUCT_LIBRARY_MIN_TOKENS", 2)
+    for what, steps, most in (("whole", steps_alone(model, cuts_whole), 192), ("changing portions", steps_alone(model, cuts_changing), 192),
+                              ("mixed", *steps_mixed(model, 3))):
+        got = replay(model, "bfloat16", steps, max_tokens=most)
+        check(model, "bfloat16", got, f"long forms, {what}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
