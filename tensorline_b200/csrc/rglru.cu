@@ -92,12 +92,47 @@ __global__ void __launch_bounds__(256) split3_kernel(const float* __restrict__ x
     }
 }
 
+// the same, eight channels of one block a thread (bw a multiple of 8, both pointers 16-byte aligned)
+__global__ void __launch_bounds__(256) split3_vec_kernel(const float* __restrict__ x, bf16* __restrict__ parts, int T, int W, int bw) {
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const size_t total = (size_t)T * W / 8;
+    const int row = W / 8;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / row), c = (int)(idx - (size_t)t * row) * 8;
+        const int blk = c / bw, j = c - blk * bw;
+        const float4 a = reinterpret_cast<const float4*>(x)[2 * idx], b = reinterpret_cast<const float4*>(x)[2 * idx + 1];
+        const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        uint4 out[3];
+        bf16* hi = reinterpret_cast<bf16*>(&out[0]);
+        bf16* mid = reinterpret_cast<bf16*>(&out[1]);
+        bf16* lo = reinterpret_cast<bf16*>(&out[2]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            hi[k] = __float2bfloat16_rn(v[k]);
+            const float r1 = v[k] - __bfloat162float(hi[k]);
+            mid[k] = __float2bfloat16_rn(r1);
+            lo[k] = __float2bfloat16_rn(r1 - __bfloat162float(mid[k]));
+        }
+        bf16* p = parts + ((size_t)blk * T + t) * 3 * bw + j;
+        *reinterpret_cast<uint4*>(p) = out[0];
+        *reinterpret_cast<uint4*>(p + bw) = out[1];
+        *reinterpret_cast<uint4*>(p + 2 * bw) = out[2];
+    }
+}
+
 TL_EXPORT int tl_split3(const float* x, void* parts, int T, int W, int blocks, cudaStream_t stream) {
     if (T <= 0 || W <= 0) return 0;
     if (blocks < 1 || W % blocks) return 1;
+    const int bw = W / blocks;
+    if (bw % 8 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(parts)) & 15) == 0) {
+        const size_t vecs = (size_t)T * W / 8;
+        const int grid = (int)min((size_t)tl_num_sms() * 8, (vecs + 255) / 256);
+        return launch_after_wait(split3_vec_kernel, dim3(grid), dim3(256), 0, stream, x, (bf16*)parts, T, W, bw);
+    }
     const size_t total = (size_t)T * W;
     const int grid = (int)min((size_t)tl_num_sms() * 8, (total + 255) / 256);
-    return launch_after_wait(split3_kernel, dim3(grid), dim3(256), 0, stream, x, (bf16*)parts, T, W, W / blocks);
+    return launch_after_wait(split3_kernel, dim3(grid), dim3(256), 0, stream, x, (bf16*)parts, T, W, bw);
 }
 
 constexpr int RG_CHUNK = 32;                             // tokens of a chunk of a long step (see rglru_chunk_kernel)
