@@ -505,12 +505,100 @@ __global__ void __launch_bounds__(256) add_rmsnorm_pair_kernel(float* __restrict
     }
 }
 
+// The fast path, as for the single norm: H a multiple of 4, a thread keeps its NV chunks of 4 values in registers, every load
+// of the row is in flight at once, x, a and b are read once.  Few rows (a decode step): the weights, nobody's output, are read
+// before the wait for the kernel in front.  Same arithmetic as above but for the order of the sum of squares.
+template <typename TA, typename TW, int NV>
+__global__ void add_rmsnorm_pair_vec_kernel(float* __restrict__ x, const TA* __restrict__ a, const TA* __restrict__ b,
+                                            const TW* __restrict__ w1, const TW* __restrict__ w2, TA* __restrict__ h1,
+                                            TA* __restrict__ h2, const int* __restrict__ rows, int H, float eps) {
+    __shared__ float red[33];
+    const int i = blockIdx.x, nvec = H >> 2;
+    float v[NV][4], wa[NV][4], wb[NV][4];
+    const bool early = gridDim.x <= 128 && NV <= 2;
+    if (early) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < nvec) {
+                Vec4<TW>::load(w1 + 4 * c, wa[k]);
+                if (h2) Vec4<TW>::load(w2 + 4 * c, wb[k]);
+            }
+        }
+    }
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    const size_t src = (size_t)(rows ? rows[i] : i) * H;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < nvec) Vec4<float>::load(x + src + 4 * c, v[k]);
+    }
+    if (a) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            const int c = threadIdx.x + k * blockDim.x;
+            if (c < nvec) {
+                float av[4], bv[4] = {0.f, 0.f, 0.f, 0.f};
+                Vec4<TA>::load(a + src + 4 * c, av);
+                if (b) Vec4<TA>::load(b + src + 4 * c, bv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[k][e] += b ? av[e] + bv[e] : av[e];
+                if (!rows) Vec4<float>::store(x + src + 4 * c, v[k]);
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+        if (threadIdx.x + k * blockDim.x < nvec)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss = fmaf(v[k][e], v[k][e], ss);
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+        const int c = threadIdx.x + k * blockDim.x;
+        if (c < nvec) {
+            if (!early) {
+                Vec4<TW>::load(w1 + 4 * c, wa[k]);
+                if (h2) Vec4<TW>::load(w2 + 4 * c, wb[k]);
+            }
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) o[e] = v[k][e] * rstd * wa[k][e];
+            Vec4<TA>::store(h1 + (size_t)i * H + 4 * c, o);
+            if (h2) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[e] = v[k][e] * rstd * wb[k][e];
+                Vec4<TA>::store(h2 + (size_t)i * H + 4 * c, o);
+            }
+        }
+    }
+}
+
+template <typename TA, typename TW>
+static void launch_add_rmsnorm_pair(float* x, const void* a, const void* b, const void* w1, const void* w2, void* h1, void* h2,
+                                    const int* rows, int R, int H, float eps, cudaStream_t stream) {
+    const int nvec = H >> 2;
+    const bool vec = (H & 3) == 0 && nvec <= 8192 &&
+                     ((((uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w1 | (uintptr_t)w2 | (uintptr_t)h1 | (uintptr_t)h2) & 15) == 0);
+#define PLAUNCH(NV) launch_after_wait(add_rmsnorm_pair_vec_kernel<TA, TW, NV>, dim3(R), dim3(((nvec + NV - 1) / NV + 31) / 32 * 32), 0, stream, \
+        x, (const TA*)a, (const TA*)b, (const TW*)w1, (const TW*)w2, (TA*)h1, (TA*)h2, rows, H, eps)
+    if (!vec) launch_after_wait(add_rmsnorm_pair_kernel<TA, TW>, dim3(R), dim3(256), 0, stream, x, (const TA*)a, (const TA*)b,
+                                (const TW*)w1, (const TW*)w2, (TA*)h1, (TA*)h2, rows, H, eps);
+    else if (nvec <= 1024) PLAUNCH(1);
+    else if (nvec <= 2048) PLAUNCH(2);
+    else if (nvec <= 4096) PLAUNCH(4);
+    else PLAUNCH(8);
+#undef PLAUNCH
+}
+
 TL_EXPORT int tl_add_rmsnorm_pair(float* x, const void* a, const void* b, const void* w1, const void* w2, int w_dtype, void* h1,
                                   void* h2, int act_dtype, const int* rows, int R, int H, float eps, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (b && !a) return 1;
-#define ARP(TA, TW) launch_after_wait(add_rmsnorm_pair_kernel<TA, TW>, dim3(R), dim3(256), 0, stream, x, (const TA*)a, (const TA*)b, \
-        (const TW*)w1, (const TW*)w2, (TA*)h1, (TA*)h2, rows, H, eps)
+#define ARP(TA, TW) launch_add_rmsnorm_pair<TA, TW>(x, a, b, w1, w2, h1, h2, rows, R, H, eps, stream)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) ARP(float, float); else ARP(float, bf16); }
     else { if (w_dtype == TL_F32) ARP(bf16, float); else ARP(bf16, bf16); }
 #undef ARP
