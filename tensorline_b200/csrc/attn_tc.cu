@@ -182,6 +182,9 @@ struct TcAttnArgs {
     int ksplit, tokens;
     float* part_o; float* part_ml;
     const float* sink;                 // [nq] or null: one more term exp(sink[h]) in every softmax denominator of head h
+    // The one-tile kernel only, with a window: the keys at positions below keep_first stay visible to every later row.
+    // Their key tiles come first in a block's walk, then the window's.
+    int keep_first;
 };
 
 // One thread's share of a 128-row Q tile, 16-byte chunks r, r + 128, ... of its BM x D / 8 chunks; row = (token, head of
@@ -273,7 +276,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     const int pos_hi = sp + (row_end - 1) / g, pos_first = sp + row0 / g;
     tl_checked(pos_hi / A.page_size, A.max_pages, A.lim, TL_K_TC_PREFILL);  // the last table entry this tile reads
     const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
-    const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN, n_kt = kt_hi - kt_lo + 1;
+    const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN;
+    // step i of the walk reads key tile i while i < n_keep (kept first keys under the window's first tile), then the window's
+    const int keep = A.window > 0 ? A.keep_first : 0;
+    const int n_keep = min((keep + BN - 1) / BN, kt_lo), n_kt = n_keep + kt_hi - kt_lo + 1;
+    auto tile_at = [&](int i) { return i < n_keep ? i : kt_lo + (i - n_keep); };
 
     if (tid == 0) {
         for (int i = 0; i < 2; ++i) {
@@ -309,7 +316,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
         }
 
         for (int i = 0; i < n_kt && ok; ++i) {
-            const int sl = i & 1, kt = kt_lo + i;
+            const int sl = i & 1, kt = tile_at(i);
             ok = mbar_wait(bar_s + sl, (i >> 1) & 1, abort_flag, A.status, 1);          // S(i) is ready
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -319,11 +326,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                 tmem_ld32(lane_addr + S_COL + sl * BN + c0, reinterpret_cast<float(&)[32]>(s[c0]));
             tmem_ld_wait();                                 // all parts in flight, one wait
             const int key0 = kt * BN;
-            if (!(key0 + BN - 1 <= pos_r && key0 >= lo_r)) {   // not every key of the tile is visible to this row
+            if (!(key0 + BN - 1 <= pos_r && (key0 >= lo_r || key0 + BN <= keep))) {   // not every key of the tile is visible to this row
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int j = key0 + c;
-                    if (!(j <= pos_r && j >= lo_r)) s[c] = -INFINITY;
+                    if (!(j <= pos_r && (j >= lo_r || j < keep))) s[c] = -INFINITY;
                 }
             }
             const float mx = row_max(s) * A.scale_log2;
@@ -457,7 +464,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                 ok = mbar_wait(bar_free + sl, ((j - 2) >> 1) & 1, abort_flag, A.status, is_k ? 9 : 10, true);
                 if (!ok) break;
             }
-            load_kv(tiles + sl * K_BYTES, pages, tab, ps_shift, page_stride, (kt_lo + j) * BN, pos_hi, lane, A.lim);
+            load_kv(tiles + sl * K_BYTES, pages, tab, ps_shift, page_stride, tile_at(j) * BN, pos_hi, lane, A.lim);
             cp_async_wait_all();
             fence_async_proxy();
             mbar_arrive(bar_full + sl);
@@ -1213,6 +1220,9 @@ TL_EXPORT int tl_attn_tc_head_dim() { return D; }
 // launchers set it before every launch, so the entry points keep their arguments.
 static const float* g_sink = nullptr;
 TL_EXPORT int tl_attn_set_sink(const float* sink) { g_sink = sink; return 0; }
+// The kept first keys of the one-tile launches that follow (0: none), set before every launch like the sink.
+static int g_keep_first = 0;
+TL_EXPORT int tl_attn_set_keep_first(int keep_first) { g_keep_first = keep_first > 0 ? keep_first : 0; return 0; }
 // 1 if this library was compiled as the checking build (-DTL_CHECK=1).
 TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 
@@ -1233,6 +1243,7 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
     }
     TcAttnArgs A{};
     A.sink = g_sink;
+    A.keep_first = window > 0 ? g_keep_first : 0;
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;

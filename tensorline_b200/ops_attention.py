@@ -85,6 +85,8 @@ def attn_tc_lib(head_dim: int):
         lib.tl_attn_tc2_prefill_split.restype = ctypes.c_int
         lib.tl_attn_set_sink.argtypes = [_P]
         lib.tl_attn_set_sink.restype = ctypes.c_int
+        lib.tl_attn_set_keep_first.argtypes = [_I]
+        lib.tl_attn_set_keep_first.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
 
@@ -103,8 +105,9 @@ def tc_min_page(head_dim: int) -> int:
 
 
 def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-               nq, nkv, d, window, scale, order=None, sink=None) -> None:
-    """Prompt-portion attention on tcgen05: 128 query rows per block, S and O in tensor memory."""
+               nq, nkv, d, window, scale, order=None, sink=None, keep_first: int = 0) -> None:
+    """Prompt-portion attention on tcgen05: 128 query rows per block, S and O in tensor memory.  `keep_first` (with a
+    window): the keys at positions below it stay visible to every later row; a block walks their key tiles first."""
     from .ops_gemm import status_word
     if page_size < tc_min_page(d) or page_size > KEY_TILE or page_size & (page_size - 1):
         raise KernelError(f"page size {page_size}: the tcgen05 attention kernel for head size {d} takes powers of two "
@@ -115,6 +118,7 @@ def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, st
     if order is not None:
         tiles = order.numel()                           # the array may leave requests out
     _set_sink(attn_tc_lib(d), sink, nq)
+    attn_tc_lib(d).tl_attn_set_keep_first(int(keep_first) if window else 0)
     _check(attn_tc_lib(d).tl_attn_tc_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                              table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
                                              nq, nkv, int(window or 0), float(scale), tiles,
@@ -409,8 +413,8 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
         # portion of a thousand rows or more whatever else is beside it (a 464-token portion beside 48 single tokens,
         # 14B head counts: 129 against 169 us); steps of mostly single tokens beside a short portion keep the 64-row
         # mma.sync tiles.
-        # (the tcgen05 kernels walk one run of keys: a window with kept first keys stays with the mma.sync tiles)
-        use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and not keep_first and \
+        # (the pair kernel walks one run of keys: a window with kept first keys takes the one-tile kernel)
+        use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and \
             (rest_rows >= 96 * len(rest) or rest_rows >= 8 * TC_QUERY_TILE)
         args = (qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                 ctx.h_q_start, nq, nkv, d, window, scale)
@@ -446,10 +450,11 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
                 ksplit = 1
         if ksplit >= 2:
             pass
-        elif use_tc and TC_PAIR and one_tile_blocks > ops.num_sms() and prefill_tc_pair(*args, order(2 * TC_QUERY_TILE), sink=sink):
+        elif use_tc and TC_PAIR and not keep_first and one_tile_blocks > ops.num_sms() and \
+                prefill_tc_pair(*args, order(2 * TC_QUERY_TILE), sink=sink):
             pass
         elif use_tc:
-            prefill_tc(*args, order(TC_QUERY_TILE), sink=sink)
+            prefill_tc(*args, order(TC_QUERY_TILE), sink=sink, keep_first=keep_first)
         else:
             prefill(*args, order(KEY_TILE), sink=sink, keep_first=keep_first)
         if singles and joined is not None:
