@@ -659,20 +659,23 @@ def test_greedy_generation_through_the_engine_and_its_scheduler(model):
         assert st["free_pages"] == st["num_pages"] and st["max_running_seen"] == 3 and (st["graph_replays"] > 0) == graphs
 
 
-@pytest.mark.parametrize("name", ["S3", "S4", "S5"])
+@pytest.mark.parametrize("name", ["S3", "S4", "S5", "S6"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_further_shapes_of_the_design(name, dtype, tmp_path):
     """Attention only (a layer without a mask, more kept tokens than the window, groups of one expert; prefixes could be
     shared); the recurrence only (no page group at all, every expert chosen); sizes that are multiples of nothing much and a
-    window of the token itself: whole requests, changing portions and a small pool against the plain model."""
+    window of the token itself; sizes that the tensor-core kernels take, with prompts of hundreds of tokens (the tcgen05 prompt
+    kernel over kept first keys, the recurrence in chunks, the gates from three parts of a float): whole requests, changing
+    portions and a small pool against the plain model."""
     folder = write_tiny_sumuvik(name, tmp_path / name)
     plain = PlainSumuvik(folder)
     V = CONFIGS[name]["vocab"]
-    reqs = {f"r{i}": random_tokens(V, n, seed=300 + i) for i, n in enumerate([3, 50, 1, 81, 33])}
+    lengths = [290, 3, 400, 130] if name == "S6" else [3, 50, 1, 81, 33]
+    reqs = {f"r{i}": random_tokens(V, n, seed=300 + i) for i, n in enumerate(lengths)}
     m = dict(name=name, folder=folder, reqs=reqs, want={r: forward(plain, t) for r, t in reqs.items()}, page=PAGE_SIZE[name], vocab=V)
-    whole = replay(m, dtype, steps_alone(m, cuts_whole), max_tokens=128)
+    whole = replay(m, dtype, steps_alone(m, cuts_whole), max_tokens=max(128, -(-max(lengths) // 64) * 64))
     check(m, dtype, whole, "whole")
-    cut = replay(m, dtype, steps_alone(m, cuts_changing), max_tokens=128)
+    cut = replay(m, dtype, steps_alone(m, cuts_changing), max_tokens=max(128, -(-max(lengths) // 64) * 64))
     check(m, dtype, cut, "changing portions")
     steps, peak = steps_mixed(m, 3, max_live=3)
     mixed = replay(m, dtype, steps, max_tokens=peak)

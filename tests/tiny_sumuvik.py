@@ -84,8 +84,17 @@ S5 = _model(101, 52, 1e-5, 7.0, [
     {"type": "rglru", "mixer": _rec(39, 3, 3), "mlp": _moe(18, 1.7, 10, 3, 5, 2, 2.0, (10, 2.2))},
     {"type": "attention", "mixer": _att(2, 1, 10, 6, 0.4, (40, 1), _rot(20.0, 4, (3.0, 1.0, 3.0, 8.0))), "mlp": None},
 ])
-CONFIGS = {"S1": S1, "S2": S2, "S3": S3, "S4": S4, "S5": S5}
-PAGE_SIZE = {"S1": 8, "S2": 16, "S3": 4, "S4": 16, "S5": 16}
+# sizes that the tensor-core kernels take (heads of 128 and 64, values narrower and wider than the keys, pages of 32), for
+# prompts of hundreds of tokens: kept tokens over two key tiles far under the window, gates of four blocks, sixteen experts
+S6 = _model(300, 192, 1e-5, 4.0, [
+    {"type": "attention", "mixer": _att(8, 2, 128, 64, 0.12, (150, 70), _rot(10000.0, 64, (8.0, 1.0, 4.0, 128.0))),
+     "mlp": _moe(48, 2.0, 16, 4, 4, 2, 2.0, (64, 1.5))},
+    {"type": "rglru", "mixer": _rec(256, 4, 4), "mlp": _dense(320, 3.0)},
+    {"type": "attention", "mixer": _att(4, 4, 64, 128, 0.2, (100, 0), _rot(1000.0, 64)), "mlp": None},
+    {"type": "rglru", "mixer": _rec(128, 2, 3), "mlp": _moe(40, 1.5, 8, 2, 2, 2, 1.0)},
+])
+CONFIGS = {"S1": S1, "S2": S2, "S3": S3, "S4": S4, "S5": S5, "S6": S6}
+PAGE_SIZE = {"S1": 8, "S2": 16, "S3": 4, "S4": 16, "S5": 16, "S6": 32}
 
 
 def write_tiny_sumuvik(name: str, folder=None, seed: int = 0, config: dict | None = None, std: float = 0.12) -> Path:
