@@ -192,6 +192,13 @@ __device__ __forceinline__ float tl_swish_clamped(float g, float u, float limit,
     u = fminf(fmaxf(u, -limit), limit);
     return (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
 }
+// The same in the bfloat16 engine (g and u hold bfloat16 values), with the division that has no special-case branch, as for
+// silu: every bfloat16 path of the clamped swish that starts from bfloat16 values calls this function and so gives the same bits.
+__device__ __forceinline__ float tl_swish_clamped_bf16(float g, float u, float limit, float alpha) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return __fdividef(g, 1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
 // act(g) * u for every code above, exact arithmetic; `limit` and `alpha` are the clamped swish's constants
 __device__ __forceinline__ float tl_act_pair(float g, float u, int act, float limit, float alpha) {
     return act == TL_ACT_SWISH_CLAMPED ? tl_swish_clamped(g, u, limit, alpha) : tl_act(g, act) * u;
@@ -203,7 +210,7 @@ __device__ __forceinline__ float tl_gate_mul(float g, float u, int kind) {
 }
 // The same with `kind` 3: the clamped swish with its two constants.
 __device__ __forceinline__ float tl_gate_mul(float g, float u, int kind, float limit, float alpha) {
-    return kind == 3 ? tl_swish_clamped(g, u, limit, alpha) : tl_gate_mul(g, u, kind);
+    return kind == 3 ? tl_swish_clamped_bf16(g, u, limit, alpha) : tl_gate_mul(g, u, kind);
 }
 
 // Programmatic dependent launch.  A kernel launched with launch_after_wait() may be placed on the SMs while

@@ -228,7 +228,8 @@ __global__ void silu_mul_kernel(const TA* __restrict__ gu, TA* __restrict__ out,
         const float g = to_f<TA>(gu[t * 2 * I + gc]);
         const float u = to_f<TA>(gu[t * 2 * I + gc + blk]);
         if (act == TL_ACT_GELU_TANH) out[idx] = from_f<TA>(tl_gelu_tanh(g) * u);
-        else if (act == TL_ACT_SWISH_CLAMPED) out[idx] = from_f<TA>(tl_swish_clamped(g, u, limit, alpha));
+        else if (act == TL_ACT_SWISH_CLAMPED)
+            out[idx] = from_f<TA>(sizeof(TA) == 4 ? tl_swish_clamped(g, u, limit, alpha) : tl_swish_clamped_bf16(g, u, limit, alpha));
         else if constexpr (sizeof(TA) == 4) out[idx] = (g / (1.0f + expf(-g))) * u;     // the 32-bit engine: exact division
         else                           out[idx] = from_f<TA>(tl_silu_mul(g, u));
     }
@@ -270,7 +271,7 @@ __global__ void __launch_bounds__(256) silu_mul_vec8_kernel(const bf16* __restri
             const float u0 = __low2float(u2[e]), u1 = __high2float(u2[e]);
             if (ACT == TL_ACT_GELU_TANH) o2[e] = __floats2bfloat162_rn(tl_gelu_tanh(g0) * u0, tl_gelu_tanh(g1) * u1);
             else if (ACT == TL_ACT_SWISH_CLAMPED)
-                o2[e] = __floats2bfloat162_rn(tl_swish_clamped(g0, u0, limit, alpha), tl_swish_clamped(g1, u1, limit, alpha));
+                o2[e] = __floats2bfloat162_rn(tl_swish_clamped_bf16(g0, u0, limit, alpha), tl_swish_clamped_bf16(g1, u1, limit, alpha));
             else o2[e] = __floats2bfloat162_rn(tl_silu_mul(g0, u0), tl_silu_mul(g1, u1));
         }
         *reinterpret_cast<uint4*>(out + t * I + cs[k]) = ov;

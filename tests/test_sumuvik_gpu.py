@@ -460,7 +460,7 @@ def test_recurrence_keeps_a_far_token(decoded):
 
 
 @pytest.mark.parametrize("E,top,groups,keep", [(8, 2, 4, 2), (6, 3, 2, 1), (9, 4, 3, 2), (4, 4, 1, 1), (4, 1, 4, 1), (10, 3, 5, 2), (64, 8, 8, 4),
-                                               (256, 8, 8, 4), (3, 3, 1, 1), (12, 3, 2, 1)])
+                                               (256, 8, 8, 4), (3, 3, 1, 1), (14, 5, 2, 1)])
 def test_choice_of_experts_among_groups(E, top, groups, keep):
     """Sigmoid scores with a correction of their own size (choice scores on both sides of zero), the best groups by the sum
     of their two largest, the largest choice scores inside them, weights from the scores without the correction."""
