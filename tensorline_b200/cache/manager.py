@@ -37,15 +37,20 @@ class PagedKV:
     """Keys and values of `num_kv_heads` heads of `head_dim`, all of them (`window` None) or
     the last `window` positions and, with `keep_first`, the first `keep_first` positions of the request as well (they
     stay readable however far the window has moved).  `shared_values`: the value of a token is its key row itself (a
-    mixer that caches one latent vector a token): one page tensor serves as both."""
+    mixer that caches one latent vector a token): one page tensor serves as both.  `chunk` (instead of a window): the
+    positions are cut into chunks of that many, counted from 0, and a query reads its own chunk only; the group is kept
+    like a window group whose window starts at the chunk's first position."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     shared_values: bool = False
     keep_first: int = 0
+    chunk: int | None = None
 
     @property
     def group_key(self):
+        if self.chunk is not None:
+            return ("paged_kv", None, 0, self.chunk)
         return ("paged_kv", self.window, self.keep_first if self.window is not None else 0)
 
 
@@ -69,6 +74,12 @@ class PageGroup:
     caches: list = field(default_factory=list)          # ids of the cache entries that use this group
     table: np.ndarray | None = None                     # [max_slots + 1, max_pages_per_seq] int32
     version: int = 0                                    # bumped at every write to `table`
+    chunk: int | None = None                            # queries read their own chunk of this many positions only
+
+    @property
+    def keeps_all(self) -> bool:
+        """Whether the group never gives a page back before its request ends."""
+        return self.window is None and self.chunk is None
 
     @property
     def scratch_page(self) -> int:
@@ -107,13 +118,15 @@ class CacheManager:
                 raise TypeError(f"cache {cid!r}: unknown need {need!r}")
             if need.window is not None and need.window < 1:
                 raise ValueError(f"cache {cid!r}: window must be positive")
+            if need.chunk is not None and (need.chunk < 1 or need.window is not None):
+                raise ValueError(f"cache {cid!r}: chunks are positive and stand instead of a window")
             g = by_key.get(need.group_key)
             if g is None:
                 n = num_pages[need.window] if isinstance(num_pages, dict) else num_pages
                 if need.keep_first < 0:
                     raise ValueError(f"cache {cid!r}: keep_first must not be negative")
                 g = PageGroup(len(self.groups), need.window, PagePool(n, False),
-                              keep_first=need.keep_first if need.window is not None else 0)
+                              keep_first=need.keep_first if need.window is not None else 0, chunk=need.chunk)
                 g.table = np.full((max_num_seqs + 1, self.max_pages_per_seq), n, dtype=np.int32)
                 by_key[need.group_key] = g
                 self.groups.append(g)
@@ -151,8 +164,8 @@ class CacheManager:
     def can_ever_hold(self, num_tokens: int) -> bool:
         """Whether a request of `num_tokens` tokens could lie in an otherwise empty cache."""
         for g in self.groups:
-            live = num_tokens if g.window is None else \
-                min(num_tokens, g.window + self.page_size + self._kept_pages(g) * self.page_size)
+            live = num_tokens if g.keeps_all else \
+                min(num_tokens, (g.window or g.chunk) + self.page_size + self._kept_pages(g) * self.page_size)
             if -(-live // self.page_size) > g.pool.num_pages:
                 return False
         return True
@@ -208,13 +221,13 @@ class CacheManager:
             return g.pool.find(digests[i], digests[i - 1] if i else None, tokens[i * ps:(i + 1) * ps]) is not None
 
         for g in self.groups:                            # groups that keep everything bound k from above
-            if g.window is None:
+            if g.keeps_all:
                 k = 0
                 while k < most and served(g, k):
                     k += 1
                 most = k
         for k in range(most, 0, -1):
-            if all(served(g, i) for g in self.groups if g.window is not None
+            if all(served(g, i) for g in self.groups if not g.keeps_all
                    for i in self._needed_pages(g, k * ps, k)):
                 return k, digests[:k]
         return 0, []
@@ -251,6 +264,8 @@ class CacheManager:
 
     def _first_needed_page(self, g: PageGroup, start: int) -> int:
         """Index of the first page a query at position >= `start` can still read through its window."""
+        if g.chunk is not None:                          # the chunk of `start` and every later one
+            return (start // g.chunk) * g.chunk // self.page_size
         if g.window is None:
             return 0
         return max(0, start - g.window + 1) // self.page_size
@@ -288,7 +303,7 @@ class CacheManager:
 
     def _release_behind_window(self, held: _Held, start: int) -> None:
         for g, pages in zip(self.groups, held.pages):
-            if g.window is None:
+            if g.keeps_all:
                 continue
             first = min(self._first_needed_page(g, start), len(pages))
             gone = [(i, p) for i, p in enumerate(pages[:first]) if p >= 0 and i >= self._kept_pages(g)]

@@ -9,6 +9,9 @@
 // key and no value that is not scaled and counts once.
 // `keep_first` (with a window): the keys at positions below it are read as well, however far the window has moved.
 // `gate` (float [T, nq], may be null): the finished row is multiplied by sigmoid(gate[t, h]).
+// `chunk` (> 0, instead of a window): the sequence is cut into chunks of that many positions counted from position 0, and
+// a query reads the keys of its own chunk only: lo = (p / chunk) * chunk.
+// `slopes` (float per query head, may be null): a key's score loses slopes[h] * (p - j), its distance from the query.
 //
 // Keys are taken in tiles of 32 aligned to absolute position 0, each lane owning one key of the
 // tile, with a running maximum and sum.  The order of every addition depends only on the
@@ -25,12 +28,13 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
                                       const int* __restrict__ pos, const int* __restrict__ req_slot,
                                       int nq, int nkv, int d, int window, float scale,
                                       const float* __restrict__ sink, int keep_first, const float* __restrict__ gate,
-                                      const TlLimits L) {
+                                      int chunk, const float* __restrict__ slopes, const TlLimits L) {
     __shared__ float qs[ATT_MAX_D];
     const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
     const int kh = h / (nq / nkv);
     const int p = pos[t];
-    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int lo = chunk > 0 ? (p / chunk) * chunk : (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const float slope = slopes ? slopes[h] : 0.f;
     const int* tab = table + (size_t)tl_checked(req_slot[t], L.table_rows, L, TL_K_TOKENWISE) * max_pages;
     const TA* qrow = q + (size_t)t * q_stride + (size_t)h * d;
     for (int e = lane; e < d; e += 32) qs[e] = to_f<TA>(qrow[e]);
@@ -57,6 +61,7 @@ __global__ void attn_tokenwise_kernel(const TA* __restrict__ q, int q_stride, TA
             float dot = 0.f;
             for (int e = 0; e < d; ++e) dot = fmaf(qs[e], to_f<TA>(kr[e]), dot);
             s = dot * scale;
+            if (slopes) s -= slope * (float)(p - j);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float alpha = expf(m - m_new);            // 0 on the first tile (m = -inf)
@@ -100,18 +105,18 @@ TL_EXPORT int tl_attn_tokenwise(const void* q, int q_stride, void* out, int act_
                                 const void* k_pages, const void* v_pages, const int* table, int max_pages,
                                 int page_size, const int* pos, const int* req_slot, int T, int nq, int nkv,
                                 int d, int window, float scale, const float* sink, int keep_first, const float* gate,
-                                int table_rows, int total_pages, int* fault, cudaStream_t stream) {
+                                int chunk, const float* slopes, int table_rows, int total_pages, int* fault, cudaStream_t stream) {
     const TlLimits L{table_rows, total_pages, fault};
     if (T <= 0) return 0;
-    if (d > ATT_MAX_D || nq % nkv) return 1;
+    if (d > ATT_MAX_D || nq % nkv || (chunk > 0 && window > 0) || chunk < 0) return 1;
     dim3 grid(T, nq);
     if (act_dtype == TL_F32)
         attn_tokenwise_kernel<float><<<grid, 32, 0, stream>>>((const float*)q, q_stride, (float*)out,
             (const float*)k_pages, (const float*)v_pages, table, max_pages, page_size, pos, req_slot,
-            nq, nkv, d, window, scale, sink, window > 0 ? keep_first : 0, gate, L);
+            nq, nkv, d, window, scale, sink, window > 0 ? keep_first : 0, gate, chunk, slopes, L);
     else
         attn_tokenwise_kernel<bf16><<<grid, 32, 0, stream>>>((const bf16*)q, q_stride, (bf16*)out,
             (const bf16*)k_pages, (const bf16*)v_pages, table, max_pages, page_size, pos, req_slot,
-            nq, nkv, d, window, scale, sink, window > 0 ? keep_first : 0, gate, L);
+            nq, nkv, d, window, scale, sink, window > 0 ? keep_first : 0, gate, chunk, slopes, L);
     return tl_launch_status();
 }

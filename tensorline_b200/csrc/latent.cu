@@ -10,7 +10,8 @@
 // Norm statistics, angles and every sum are float.
 #include "common.cuh"
 
-// rotation of pair (i, i + rot/2) of the first `rot` of n values at position p; values past rot pass through
+// rotation of one pair of the first `rot` of n values at position p (pair i is (i, i + rot/2), or with `interleaved`
+// (2i, 2i + 1)); values past rot pass through
 __device__ __forceinline__ void turn_pair(float a, float b, int p, float f, float& ra, float& rb) {
     float s, c;
     sincosf(__fmul_rn((float)p, f), &s, &c);
@@ -18,24 +19,26 @@ __device__ __forceinline__ void turn_pair(float a, float b, int p, float f, floa
     rb = __fmul_rn(b, c) + __fmul_rn(a, s);
 }
 
-// down: float [T, qr + rank + dr] (query latent, key/value latent, shared key part).  cq: [T, qr]; the page row: d wide.
+// down: float rows `ld` apart, each [qr + rank + dr ...] (query latent, key/value latent, shared key part, then whatever else
+// rode in the same product).  cq: [T, qr]; the page row: d wide.
 template <typename TA, typename TW>
-__global__ void __launch_bounds__(256) latent_prep_kernel(const float* __restrict__ down, int qr, int rank, int dr, const TW* __restrict__ wq,
+__global__ void __launch_bounds__(256) latent_prep_kernel(const float* __restrict__ down, int ld, int qr, int rank, int dr, const TW* __restrict__ wq,
                                                           const TW* __restrict__ wkv, float eps, const float* __restrict__ inv_freq, int rot,
                                                           const int* __restrict__ pos, const int* __restrict__ req_slot,
                                                           const int* __restrict__ table, int max_pages, int page_size,
-                                                          TA* __restrict__ cq, TA* __restrict__ k_pages, int d, int write_kv, const TlLimits L) {
+                                                          TA* __restrict__ cq, TA* __restrict__ k_pages, int d, int write_kv, int interleaved,
+                                                          const TlLimits L) {
     __shared__ float red[33];
     const int t = blockIdx.x;
     grid_dependency_wait();
     grid_dependency_trigger();
-    const float* row = down + (size_t)t * (qr + rank + dr);
+    const float* row = down + (size_t)t * ld;
     float sq = 0.f, sk = 0.f;
     for (int i = threadIdx.x; i < qr; i += blockDim.x) sq = fmaf(row[i], row[i], sq);
     for (int i = threadIdx.x; i < rank; i += blockDim.x) sk = fmaf(row[qr + i], row[qr + i], sk);
-    sq = block_sum(sq, red);
+    if (qr > 0) sq = block_sum(sq, red);                 // qr 0: the queries come from a projection of their own, no latent
     sk = block_sum(sk, red);
-    const float rq = 1.0f / sqrtf(sq / (float)qr + eps), rk = 1.0f / sqrtf(sk / (float)rank + eps);
+    const float rq = qr > 0 ? 1.0f / sqrtf(sq / (float)qr + eps) : 0.f, rk = 1.0f / sqrtf(sk / (float)rank + eps);
     for (int i = threadIdx.x; i < qr; i += blockDim.x) cq[(size_t)t * qr + i] = from_f<TA>(row[i] * rq * to_f<TW>(wq[i]));
     if (!write_kv) return;
     const int p = pos[t];
@@ -48,22 +51,23 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(const float* __restric
     const int rhalf = rot >> 1;
     for (int i = threadIdx.x; i < rhalf; i += blockDim.x) {
         float a, b;
-        turn_pair(r[i], r[i + rhalf], p, inv_freq[i], a, b);
-        dst[rank + i] = from_f<TA>(a); dst[rank + i + rhalf] = from_f<TA>(b);
+        const int e1 = interleaved ? 2 * i : i, e2 = interleaved ? 2 * i + 1 : i + rhalf;
+        turn_pair(r[e1], r[e2], p, inv_freq[i], a, b);
+        dst[rank + e1] = from_f<TA>(a); dst[rank + e2] = from_f<TA>(b);
     }
     for (int i = rot + threadIdx.x; i < dr; i += blockDim.x) dst[rank + i] = from_f<TA>(r[i]);
     for (int i = rank + dr + threadIdx.x; i < d; i += blockDim.x) dst[i] = from_f<TA>(0.f);
 }
 
-TL_EXPORT int tl_latent_prep(const float* down, int qr, int rank, int dr, const void* wq, const void* wkv, int w_dtype, float eps,
+TL_EXPORT int tl_latent_prep(const float* down, int ld, int qr, int rank, int dr, const void* wq, const void* wkv, int w_dtype, float eps,
                              const float* inv_freq, int rot, const int* pos, const int* req_slot, const int* table, int max_pages,
-                             int page_size, void* cq, void* k_pages, int act_dtype, int d, int write_kv, int T, int table_rows,
-                             int total_pages, int* fault, cudaStream_t stream) {
+                             int page_size, void* cq, void* k_pages, int act_dtype, int d, int write_kv, int T, int interleaved,
+                             int table_rows, int total_pages, int* fault, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if ((rot & 1) || rot > dr || rank + dr > d) return 1;
+    if ((rot & 1) || rot > dr || rank + dr > d || ld < qr + rank + dr) return 1;
     const TlLimits L{table_rows, total_pages, fault};
-#define LP(TA, TW) launch_after_wait(latent_prep_kernel<TA, TW>, dim3(T), dim3(256), 0, stream, down, qr, rank, dr, (const TW*)wq, (const TW*)wkv, \
-        eps, inv_freq, rot, pos, req_slot, table, max_pages, page_size, (TA*)cq, (TA*)k_pages, d, write_kv, L)
+#define LP(TA, TW) launch_after_wait(latent_prep_kernel<TA, TW>, dim3(T), dim3(256), 0, stream, down, ld, qr, rank, dr, (const TW*)wq, (const TW*)wkv, \
+        eps, inv_freq, rot, pos, req_slot, table, max_pages, page_size, (TA*)cq, (TA*)k_pages, d, write_kv, interleaved, L)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) LP(float, float); else LP(float, bf16); }
     else { if (w_dtype == TL_F32) LP(bf16, float); else LP(bf16, bf16); }
 #undef LP
@@ -74,7 +78,7 @@ TL_EXPORT int tl_latent_prep(const float* down, int qr, int rank, int dr, const 
 // columns from rank + dr on zeros.
 template <typename TA>
 __global__ void latent_qrot_kernel(const TA* __restrict__ q, int dk, int dr, const float* __restrict__ inv_freq, int rot,
-                                   const int* __restrict__ pos, TA* __restrict__ qa, int rank, int d, int H) {
+                                   const int* __restrict__ pos, TA* __restrict__ qa, int rank, int d, int H, int interleaved) {
     const int t = blockIdx.x, h = blockIdx.y;
     grid_dependency_wait();
     grid_dependency_trigger();
@@ -83,19 +87,20 @@ __global__ void latent_qrot_kernel(const TA* __restrict__ q, int dk, int dr, con
     const int p = pos[t], rhalf = rot >> 1;
     for (int i = threadIdx.x; i < rhalf; i += blockDim.x) {
         float a, b;
-        turn_pair(to_f<TA>(src[i]), to_f<TA>(src[i + rhalf]), p, inv_freq[i], a, b);
-        dst[i] = from_f<TA>(a); dst[i + rhalf] = from_f<TA>(b);
+        const int e1 = interleaved ? 2 * i : i, e2 = interleaved ? 2 * i + 1 : i + rhalf;
+        turn_pair(to_f<TA>(src[e1]), to_f<TA>(src[e2]), p, inv_freq[i], a, b);
+        dst[e1] = from_f<TA>(a); dst[e2] = from_f<TA>(b);
     }
     for (int i = rot + threadIdx.x; i < dr; i += blockDim.x) dst[i] = src[i];
     for (int i = dr + threadIdx.x; i < d - rank; i += blockDim.x) dst[i] = from_f<TA>(0.f);
 }
 
 TL_EXPORT int tl_latent_qrot(const void* q, int dk, int dr, const float* inv_freq, int rot, const int* pos, void* qa, int rank, int d,
-                             int H, int T, int act_dtype, cudaStream_t stream) {
+                             int H, int T, int act_dtype, int interleaved, cudaStream_t stream) {
     if (T <= 0 || H <= 0) return 0;
     if ((rot & 1) || rot > dr || rank + dr > d || H > 65535) return 1;
-    if (act_dtype == TL_F32) launch_after_wait(latent_qrot_kernel<float>, dim3(T, H), dim3(64), 0, stream, (const float*)q, dk, dr, inv_freq, rot, pos, (float*)qa, rank, d, H);
-    else launch_after_wait(latent_qrot_kernel<bf16>, dim3(T, H), dim3(64), 0, stream, (const bf16*)q, dk, dr, inv_freq, rot, pos, (bf16*)qa, rank, d, H);
+    if (act_dtype == TL_F32) launch_after_wait(latent_qrot_kernel<float>, dim3(T, H), dim3(64), 0, stream, (const float*)q, dk, dr, inv_freq, rot, pos, (float*)qa, rank, d, H, interleaved);
+    else launch_after_wait(latent_qrot_kernel<bf16>, dim3(T, H), dim3(64), 0, stream, (const bf16*)q, dk, dr, inv_freq, rot, pos, (bf16*)qa, rank, d, H, interleaved);
     return tl_launch_status();
 }
 

@@ -166,7 +166,7 @@ TL_EXPORT int tl_topk_softmax(const float* z, int ldz, int E, int top, int* idx,
 // by their sum (+ 1e-20), times `scale`.  E <= 1024, top <= 32.  Shared memory: c [E], s [E], the groups' scores [groups].
 __global__ void __launch_bounds__(32) route_groups_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ correction,
                                                           int E, int top, int groups, int keep, int gtop, float scale,
-                                                          int* __restrict__ idx, float* __restrict__ wts) {
+                                                          int* __restrict__ idx, float* __restrict__ wts, int softmax) {
     extern __shared__ float sm[];
     float* c = sm;
     float* s = sm + E;
@@ -175,8 +175,15 @@ __global__ void __launch_bounds__(32) route_groups_kernel(const float* __restric
     grid_dependency_wait();
     grid_dependency_trigger();
     const float* row = z + (size_t)t * ldz;
+    float top_z = -INFINITY, total = 0.f;                // softmax: the scores are the shares of all entries' exponentials
+    if (softmax) {
+        for (int e = lane; e < E; e += 32) top_z = fmaxf(top_z, row[e]);
+        top_z = warp_max(top_z);
+        for (int e = lane; e < E; e += 32) total += expf(row[e] - top_z);
+        total = warp_sum(total);
+    }
     for (int e = lane; e < E; e += 32) {
-        const float sv = 1.0f / (1.0f + expf(-row[e]));
+        const float sv = softmax ? expf(row[e] - top_z) / total : 1.0f / (1.0f + expf(-row[e]));
         s[e] = sv;
         c[e] = sv + (correction ? correction[e] : 0.f);
     }
@@ -240,13 +247,13 @@ __global__ void __launch_bounds__(32) route_groups_kernel(const float* __restric
     if (lane < top) wts[(size_t)t * top + lane] = mine / (sum + 1e-20f) * scale;
 }
 
-TL_EXPORT int tl_route_groups(const float* z, int ldz, const float* correction, int E, int top, int groups, int keep, int gtop,
+TL_EXPORT int tl_route_groups(const float* z, int ldz, const float* correction, int E, int top, int groups, int keep, int gtop, int softmax,
                               float scale, int* idx, float* wts, int T, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E > 1024 || top > 32 || top < 1 || groups < 1 || E % groups || keep < 1 || keep > groups || gtop < 1 ||
         top > keep * (E / groups)) return 1;
     const size_t smem = ((size_t)2 * E + groups) * sizeof(float);
-    launch_after_wait(route_groups_kernel, dim3(T), dim3(32), smem, stream, z, ldz, correction, E, top, groups, keep, gtop, scale, idx, wts);
+    launch_after_wait(route_groups_kernel, dim3(T), dim3(32), smem, stream, z, ldz, correction, E, top, groups, keep, gtop, scale, idx, wts, softmax);
     return tl_launch_status();
 }
 
@@ -259,12 +266,13 @@ constexpr int MOE_DOWN_ROWS = 4;                         // output rows a block 
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, const TW* __restrict__ w_up, const int* __restrict__ idx,
                                                      TA* __restrict__ a, int K, int F, int top, int gated, int act,
-                                                     const float* __restrict__ in_scale, float limit, float alpha) {
+                                                     const float* __restrict__ in_scale, float limit, float alpha, int n_real) {
     extern __shared__ __align__(16) float xs[];
     const int pair = blockIdx.x, t = pair / top, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     grid_dependency_wait();                              // launched as a dependent: nothing of another kernel is touched before this
     grid_dependency_trigger();
     const int e = idx[pair];
+    if (e >= n_real) return;                             // an identity entry: its output is the token's row itself (moe_down)
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_f<TA>(h[(size_t)t * K + k]);
     __syncthreads();
     const TW* w = w_up + (size_t)e * F * K * (gated ? 2 : 1);
@@ -291,7 +299,8 @@ __global__ void __launch_bounds__(128) moe_up_kernel(const TA* __restrict__ h, c
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a, const TW* __restrict__ w_down, const int* __restrict__ idx,
                                                        const float* __restrict__ wts, TA* __restrict__ y, int F, int N, int top,
-                                                       const TA* __restrict__ extra, const float* __restrict__ extra_gate, int ldg) {
+                                                       const TA* __restrict__ extra, const float* __restrict__ extra_gate, int ldg,
+                                                       int n_real, const TA* __restrict__ same) {
     extern __shared__ __align__(16) float xs[];          // [4 warps][F], then red [top][4]
     float* red = xs + 4 * (size_t)F;
     const int t = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -301,6 +310,10 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a,
     grid_dependency_trigger();
     for (int j = wid; j < top; j += 4) {
         const int e = idx[(size_t)t * top + j];
+        if (e >= n_real) {                               // an identity entry: the token's own row (`same` [T, N]) stands for the product
+            if (lane < 4) red[j * 4 + lane] = lane < rows ? to_f<TA>(same[(size_t)t * N + n0 + lane]) : 0.f;
+            continue;
+        }
         __syncwarp();
         for (int k = lane; k < F; k += 32) mine[k] = to_f<TA>(a[((size_t)t * top + j) * F + k]);
         __syncwarp();
@@ -322,14 +335,15 @@ __global__ void __launch_bounds__(128) moe_down_kernel(const TA* __restrict__ a,
 }
 
 TL_EXPORT int tl_moe_up(const void* h, int act_dtype, const void* w_up, int w_dtype, const int* idx, void* a, int P, int K,
-                        int F, int top, int gated, int act, const float* in_scale, float limit, float alpha, cudaStream_t stream) {
+                        int F, int top, int gated, int act, const float* in_scale, float limit, float alpha, int n_real,
+                        cudaStream_t stream) {
     if (P <= 0) return 0;
     if (act == TL_ACT_SWISH_CLAMPED && !gated) return 1;
     const size_t smem = (size_t)K * sizeof(float);
     if (smem > 48 * 1024) return 1;
     const dim3 grid(P, (F + MOE_ROWS - 1) / MOE_ROWS);
     if (grid.y > 65535) return 1;
-#define MU(TA, TW) launch_after_wait(moe_up_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top, gated, act, in_scale, limit, alpha)
+#define MU(TA, TW) launch_after_wait(moe_up_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)h, (const TW*)w_up, idx, (TA*)a, K, F, top, gated, act, in_scale, limit, alpha, n_real)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MU(float, float); else MU(float, bf16); }
     else { if (w_dtype == TL_F32) MU(bf16, float); else MU(bf16, bf16); }
 #undef MU
@@ -338,13 +352,13 @@ TL_EXPORT int tl_moe_up(const void* h, int act_dtype, const void* w_up, int w_dt
 
 TL_EXPORT int tl_moe_down(const void* a, int act_dtype, const void* w_down, int w_dtype, const int* idx, const float* wts,
                           void* y, int T, int F, int N, int top, const void* extra, const float* extra_gate, int ldg,
-                          cudaStream_t stream) {
+                          int n_real, const void* same, cudaStream_t stream) {
     if (T <= 0) return 0;
     const size_t smem = ((size_t)4 * F + (size_t)top * 4) * sizeof(float);
     if (smem > 48 * 1024) return 1;
     const dim3 grid(T, (N + MOE_DOWN_ROWS - 1) / MOE_DOWN_ROWS);
     if (grid.y > 65535) return 1;
-#define MD(TA, TW) launch_after_wait(moe_down_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)a, (const TW*)w_down, idx, wts, (TA*)y, F, N, top, (const TA*)extra, extra_gate, ldg)
+#define MD(TA, TW) launch_after_wait(moe_down_kernel<TA, TW>, grid, dim3(128), smem, stream, (const TA*)a, (const TW*)w_down, idx, wts, (TA*)y, F, N, top, (const TA*)extra, extra_gate, ldg, n_real, (const TA*)same)
     if (act_dtype == TL_F32) { if (w_dtype == TL_F32) MD(float, float); else MD(float, bf16); }
     else { if (w_dtype == TL_F32) MD(bf16, float); else MD(bf16, bf16); }
 #undef MD

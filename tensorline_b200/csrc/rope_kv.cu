@@ -12,7 +12,8 @@
 // Two options of other position encodings and mixers are arguments, not copies of the kernel: the pairing of
 // the rotated dimensions (`interleaved`: pair i is dimensions (2i, 2i + 1) instead of (i, i + rot/2)), and an
 // RMS norm of every q and k head over its d dimensions with a weight of its own (`q_norm`, `k_norm`, `norm_eps`),
-// applied after the bias and before the rotation, statistics in float.
+// applied after the bias and before the rotation, statistics in float.  `norm_dim` (0: d) is the number of dimensions the
+// mean of squares is taken over: a head padded with zeros to d is normalised over its own size.
 #include "common.cuh"
 
 // grid (T, heads): one block per (token, head), one thread per pair of dimensions, so that all loads
@@ -24,7 +25,7 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
                                const float* __restrict__ inv_freq, int rot, int nq, int nkv, int d,
                                TA* __restrict__ k_pages, TA* __restrict__ v_pages, int interleaved,
                                const float* __restrict__ q_norm, const float* __restrict__ k_norm, float norm_eps,
-                               const TlLimits L) {
+                               int norm_dim, const TlLimits L) {
     __shared__ float red[33];
     const int t = blockIdx.x, hh = blockIdx.y;
     const int p = pos[t];
@@ -50,7 +51,7 @@ __global__ void rope_kv_kernel(TA* __restrict__ qkv, const TW* __restrict__ bias
             ss = fmaf(v, v, ss);
         }
         ss = block_sum(ss, red);
-        rstd = 1.0f / sqrtf(ss / (float)d + norm_eps);
+        rstd = 1.0f / sqrtf(ss / (float)(norm_dim > 0 ? norm_dim : d) + norm_eps);
     }
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         int e1, e2;
@@ -187,7 +188,7 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
                                int page_size, const float* inv_freq, int rot, int nq, int nkv, int d,
                                void* k_pages, void* v_pages, int write_kv, int T, const float* pieces, int splits,
                                long long plane, int interleaved, const float* q_norm, const float* k_norm,
-                               float norm_eps, int table_rows, int total_pages, int* fault, cudaStream_t stream) {
+                               float norm_eps, int norm_dim, int table_rows, int total_pages, int* fault, cudaStream_t stream) {
     const TlLimits L{table_rows, total_pages, fault};
     if (T <= 0) return 0;
     if (rot < 0 || rot > d || (rot & 1) || (d & 1)) return 1;     // cudaErrorInvalidValue
@@ -212,7 +213,7 @@ TL_EXPORT int tl_rope_kv_write(void* qkv, int act_dtype, const void* bias, int b
     const int threads = half < 256 ? ((half + 31) / 32) * 32 : 256;
 #define LAUNCH(TA, TW) rope_kv_kernel<TA, TW><<<grid, threads, 0, stream>>>( \
         (TA*)qkv, (const TW*)bias, pos, req_slot, table, max_pages, page_size, inv_freq, rot, nq, nkv, d, \
-        (TA*)k_pages, (TA*)v_pages, interleaved, q_norm, k_norm, norm_eps, L)
+        (TA*)k_pages, (TA*)v_pages, interleaved, q_norm, k_norm, norm_eps, norm_dim, L)
     if (act_dtype == TL_F32) { if (bias_dtype == TL_F32) LAUNCH(float, float); else LAUNCH(float, bf16); }
     else                     { if (bias_dtype == TL_F32) LAUNCH(bf16, float);  else LAUNCH(bf16, bf16); }
 #undef LAUNCH

@@ -17,12 +17,14 @@ from ..config.qwen2 import Qwen2Config
 from ..config.vutesun import VutesunConfig
 from ..config.dekerax import DekeraxConfig
 from ..config.sumuvik import SumuvikConfig
+from ..config.tenalorn import TenalornConfig
 from ..parts import Runtime
 from ..weights import load_weights
 from .qwen2 import describe_qwen2
 from .vutesun import describe_vutesun
 from .dekerax import describe_dekerax
 from .sumuvik import describe_sumuvik
+from .tenalorn import describe_tenalorn
 from .spec import Model
 
 
@@ -54,6 +56,7 @@ register_architecture("Qwen2ForCausalLM", Qwen2Config, describe_qwen2)
 register_architecture("Vutesun", VutesunConfig, describe_vutesun)
 register_architecture("Dekerax", DekeraxConfig, describe_dekerax)
 register_architecture("Sumuvik", SumuvikConfig, describe_sumuvik)
+register_architecture("Tenalorn", TenalornConfig, describe_tenalorn)
 
 
 def load_config(folder):

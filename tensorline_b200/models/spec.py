@@ -53,6 +53,8 @@ class ModelSpec:
     stream_rows: int = 0                              # > 0: a table [rows, hidden] of vectors that run entries add to the stream
     stream_rows_name: str = "model.stream_rows"       # (`RunEntry.add_row`: a pass over shared layers announces its number)
     stream_rows_eps: float = 1e-6                     # eps of the norms the addend travels to (they fold it into their kernel)
+    streams: int = 1                                  # > 1: the residual stream is that many copies side by side, [T, streams * hidden]
+                                                      # (blocks of kind "hyper_connections"; the model's norm reads their sum)
 
 
 class Model:
@@ -60,7 +62,8 @@ class Model:
 
     def __init__(self, spec: ModelSpec, rt: Runtime):
         self.spec, self.rt = spec, rt
-        self.embedding = EMBEDDINGS.build(spec.embedding, rt, vocab=spec.vocab_size, dim=spec.hidden_size)
+        extra = {"copies": spec.streams} if spec.streams != 1 else {}
+        self.embedding = EMBEDDINGS.build(spec.embedding, rt, vocab=spec.vocab_size, dim=spec.hidden_size, **extra)
         self.blocks = [BLOCKS.build(l.block, rt) for l in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, rt)
         self.head = HEADS.build(spec.head, rt, vocab=spec.vocab_size, dim=spec.hidden_size, tied=spec.tie_word_embeddings)
@@ -109,6 +112,9 @@ class Model:
     def cache_needs(self) -> dict:
         """cache id (= index of the owning run entry) -> need."""
         needs = {}
+        own = getattr(self.embedding, "cache_need", None)
+        if own is not None and own() is not None:        # an embedding that keeps something of a request between steps
+            needs["embedding"] = own()
         for i, e in enumerate(self.spec.run):
             if e.reads_cache_of is None:
                 need = self.blocks[e.layer].cache_need()
@@ -139,7 +145,10 @@ class Model:
     # ---- one step
     def forward(self, ctx, caches: dict) -> torch.Tensor:
         """Logits [R, V] float32 at the rows `ctx.want_rows`; `caches`: cache id -> view."""
-        x = self.embedding.forward(ctx.ids)
+        if "embedding" in caches:
+            x = self.embedding.forward(ctx.ids, ctx, caches["embedding"])
+        else:
+            x = self.embedding.forward(ctx.ids)
         if self.embedding_position is not None:
             self.embedding_position.on_embedding(x, ctx)
         if self.embedding_norm is not None:

@@ -14,7 +14,7 @@ import torch
 from .csrc.build import CHECK_BUILD, load_library
 
 CORE_SOURCES = ["elementwise.cu", "rope_kv.cu", "attn_tokenwise.cu", "gemm_f32.cu", "sampling.cu", "recurrent.cu", "moe.cu",
-                "delta.cu", "latent.cu", "rglru.cu"]
+                "delta.cu", "latent.cu", "rglru.cu", "streams.cu"]
 
 _P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
@@ -26,8 +26,8 @@ _SIGNATURES = {
     "tl_head_gate": [_P, _I, _P, _I, _I, _I, _P],
     "tl_post_norm_add_norm": [_P, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _F, _I, _P],
     "tl_rope_kv_write": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _I, ctypes.c_longlong,
-                         _I, _P, _P, _F, _I, _I, _P, _P],
-    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _P, _I, _I, _P, _P],
+                         _I, _P, _P, _F, _I, _I, _I, _P, _P],
+    "tl_attn_tokenwise": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _I, _P, _I, _P, _I, _I, _P, _P],
     "tl_gemm_f32": [_P, _I, _P, _I, _I, _P, _P, _I, _I, _I, _I, _P],
     "tl_argmax": [_P, _I, _I, _I, _P, _P, _P],
     "tl_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P],
@@ -39,13 +39,13 @@ _SIGNATURES = {
     "tl_sum_normed": [_P, _P, _P, _P, _I, _P, _I, _I, _I, _F, _F, _P],
     "tl_small_proj": [_P, _I, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "tl_topk_softmax": [_P, _I, _I, _I, _P, _P, _I, _I, _P],
-    "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _F, _P],
-    "tl_route_groups": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P],
+    "tl_moe_up": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _F, _F, _I, _P],
+    "tl_route_groups": [_P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _P, _P, _I, _P],
     "tl_causal_conv": [_P, _I, _I, _P, _P, _P, _I, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _P],
     "tl_rglru_scan": [_P, _P, _P, _P, _I, _I, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _F, _I, _P, _I, ctypes.c_longlong, ctypes.c_longlong, _P],
     "tl_split3": [_P, _P, _I, _I, _I, _P],
     "tl_rglru_chunk": [],
-    "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P],
+    "tl_moe_down": [_P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P],
     "tl_moe_sort": [_P, _I, _I, _P, _P, _P, _P],
     "tl_moe_gather": [_P, _I, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P, _P],
     "tl_relu_square": [_P, _I, ctypes.c_longlong, _P],
@@ -54,8 +54,13 @@ _SIGNATURES = {
     "tl_delta_scan": [_P, _I, _I, _I, _I, _P, _I, _P, _P, _P, ctypes.c_longlong, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "tl_delta_state_floats": [_I, _I],
     "tl_delta_columns": [],
-    "tl_latent_prep": [_P, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
-    "tl_latent_qrot": [_P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _P],
+    "tl_latent_prep": [_P, _I, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _P, _I, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+    "tl_latent_qrot": [_P, _I, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "tl_embed_streams": [_P, _P, _I, _P, _I, _I, _F, _I, _P, _I, _I, _I, _P, _P, _P, _P],
+    "tl_remember_last": [_P, _P, _P, _I, _P, _P],
+    "tl_stream_step": [_P, _I, _I, _P, _F, _P, _F, _I, _P, _P, _P, _P, _I, _F, _P, _P, _P, _I, _I, _P],
+    "tl_softcap": [_P, ctypes.c_longlong, _F, _P],
+    "tl_sigmoid_gate": [_P, _P, _I, _P, _I, _I, _I, _P],
     "tl_head_matmul": [_P, _I, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _P],
 }
 
@@ -260,6 +265,89 @@ def embed(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float 
     _check(core().tl_embed(_ptr(x), _ptr(table), dtype_code(table.dtype), _ptr(ids), T, H, float(scale), _stream()), "embed")
 
 
+def embed_streams(x: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0, copies: int = 1,
+                  pairs: torch.Tensor | None = None, mul_prev: int = 0, mul_cur: int = 0, pos: torch.Tensor | None = None,
+                  req_slot: torch.Tensor | None = None, last_token: torch.Tensor | None = None) -> None:
+    """x[t] = `copies` times side by side: table[ids[t]] * scale (+ pairs[row]), x float32 [T, copies * H].  `pairs`
+    [buckets + 1, H] of the table's type: row = (previous token * mul_prev + ids[t] * mul_cur) mod buckets, and row `buckets`
+    at position 0; the previous token is ids[t - 1] if that row belongs to the same request slot, else last_token[slot]
+    (int32, one number a request slot: what `remember_last` left there in the step before)."""
+    T, H = ids.numel(), table.shape[1]
+    if x.dtype != torch.float32 or x.shape != (T, copies * H) or copies < 1:
+        raise KernelError("embed_streams: x must be float32 [T, copies * H] matching the table and ids")
+    _contig(x, "x"); _contig(table, "table"); _ints(ids, "ids")
+    buckets = 0
+    if pairs is not None:
+        buckets = pairs.shape[0] - 1
+        if pairs.dim() != 2 or pairs.shape[1] != H or pairs.dtype != table.dtype or buckets < 1:
+            raise KernelError("embed_streams: pairs must be [buckets + 1, H] of the table's type")
+        if pos is None or req_slot is None or last_token is None:
+            raise KernelError("embed_streams: a table of pairs needs positions, request slots and the slots' last tokens")
+        _contig(pairs, "pairs"); _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(last_token, "last_token")
+    _check(core().tl_embed_streams(_ptr(x), _ptr(table), dtype_code(table.dtype), _ptr(ids), T, H, float(scale), int(copies),
+                                   _ptr(pairs), buckets, int(mul_prev), int(mul_cur), _ptr(pos), _ptr(req_slot), _ptr(last_token),
+                                   _stream()), "embed_streams")
+
+
+def remember_last(ids: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, last_token: torch.Tensor, B: int) -> None:
+    """last_token[slots[b]] = the last of request b's ids in this step (its rows are q_start[b] .. q_start[b + 1] - 1)."""
+    _ints(ids, "ids"); _ints(q_start, "q_start"); _ints(slots, "slots"); _ints(last_token, "last_token")
+    if q_start.numel() < B + 1 or slots.numel() < B:
+        raise KernelError("remember_last: q_start [B + 1], slots [B]")
+    _check(core().tl_remember_last(_ptr(ids), _ptr(q_start), _ptr(slots), int(B), _ptr(last_token), _stream()), "remember_last")
+
+
+def stream_step(x: torch.Tensor, S: int, a: torch.Tensor | None = None, alpha: float = 1.0, b: torch.Tensor | None = None,
+                beta: float = 1.0, mix: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                read: torch.Tensor | None = None, w: torch.Tensor | None = None, eps: float = 0.0, h: torch.Tensor | None = None,
+                u: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> None:
+    """One boundary between sublayers of a residual stream kept as S copies, x float32 [T, S * W], in one kernel:
+    with `mix` (float32 [S, S], indexed [from, to]) and `out` (float32 [S]) every stream is rebuilt from the old ones,
+    x_r <- sum_s mix[s, r] x_s + out[r] (alpha a + beta b)  (a, b [T, W] of the activation type, either may be None); then
+    u = sum_r read[r] x_r (`read` float32 [S]; None: the plain sum) goes to `u` (float32 [R, W]) if given, and its RMS norm
+    times `w` to `h` ([R, W] of the activation type) if given.  `rows` (int32 [R]) picks rows; x is then left alone."""
+    T = x.shape[0]
+    if x.dtype != torch.float32 or x.dim() != 2 or x.shape[1] % S or not x.is_contiguous():
+        raise KernelError("stream_step: x must be float32 [T, S * W], contiguous")
+    W = x.shape[1] // S
+    R = T if rows is None else rows.numel()
+    act = h.dtype if h is not None else (a.dtype if a is not None else (b.dtype if b is not None else torch.float32))
+    for name, t in (("a", a), ("b", b)):
+        if t is not None and (t.shape != (T, W) or t.dtype != act or not t.is_contiguous()):
+            raise KernelError(f"stream_step: {name} must be [T, W] of the activation type, contiguous")
+    if (mix is None) != (out is None) or (mix is None and (a is not None or b is not None)):
+        raise KernelError("stream_step: mix and out come together, and the addends with them")
+    for name, t, n in (("mix", mix, S * S), ("out", out, S), ("read", read, S)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise KernelError(f"stream_step: {name} must be float32 with {n} numbers")
+    if h is not None and (h.shape != (R, W) or w is None or w.numel() != W or not h.is_contiguous() or not w.is_contiguous()):
+        raise KernelError("stream_step: h [R, W] comes with a weight [W]")
+    if u is not None and (u.shape != (R, W) or u.dtype != torch.float32 or not u.is_contiguous()):
+        raise KernelError("stream_step: u must be float32 [R, W]")
+    if rows is not None:
+        _ints(rows, "rows")
+    _check(core().tl_stream_step(_ptr(x), S, W, _ptr(a), float(alpha), _ptr(b), float(beta), dtype_code(act), _ptr(mix), _ptr(out),
+                                 _ptr(read), _ptr(w), dtype_code(w.dtype) if w is not None else 0, float(eps), _ptr(h), _ptr(u),
+                                 _ptr(rows), R, int(rows is None), _stream()), "stream_step")
+
+
+def softcap(z: torch.Tensor, cap: float) -> None:
+    """z <- cap * tanh(z / cap) in place, z float32."""
+    if z.dtype != torch.float32 or not z.is_contiguous():
+        raise KernelError("softcap: z must be float32, contiguous")
+    _check(core().tl_softcap(_ptr(z), z.numel(), float(cap), _stream()), "softcap")
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> None:
+    """y[t, c] = o[t, c] * sigmoid(gate[t, c]); o, y [T, N] of one type, gate float32 [T, N] (a column range of a wider
+    tensor may be passed)."""
+    T, N = o.shape
+    if y.shape != o.shape or y.dtype != o.dtype or gate.dtype != torch.float32 or gate.shape != o.shape or gate.stride(1) != 1:
+        raise KernelError("sigmoid_gate: o, y [T, N] of one type, gate float32 [T, N]")
+    _contig(o, "o"); _contig(y, "y")
+    _check(core().tl_sigmoid_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(y), T, N, dtype_code(o.dtype), _stream()), "sigmoid_gate")
+
+
 def add_rmsnorm(x: torch.Tensor, r: torch.Tensor | None, w: torch.Tensor, out: torch.Tensor, eps: float,
                 rows: torch.Tensor | None = None, write_x: bool = True, pieces: torch.Tensor | None = None,
                 alpha: float = 1.0, cast_first: bool = True) -> None:
@@ -401,11 +489,12 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tenso
                   table: torch.Tensor, page_size: int, inv_freq: torch.Tensor, rot: int, nq: int, nkv: int,
                   d: int, k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, write_kv: bool = True,
                   pieces: torch.Tensor | None = None, pairing: str = "half", q_norm: torch.Tensor | None = None,
-                  k_norm: torch.Tensor | None = None, norm_eps: float = 0.0) -> None:
+                  k_norm: torch.Tensor | None = None, norm_eps: float = 0.0, norm_dim: int = 0) -> None:
     """Bias, rotary encoding of q and k in place, and the write of k, v into their pages.
     `pairing`: "half" rotates dimensions (i, i + rot/2), "interleaved" (2i, 2i + 1).  `q_norm`, `k_norm`
     (float32 [d], both or neither): every q and k head is RMS-normalised over its d dimensions (after the
-    bias, before the rotation; statistics in float32) and multiplied by the weight.
+    bias, before the rotation; statistics in float32) and multiplied by the weight.  `norm_dim` (0: d): the mean of squares
+    is taken over this many dimensions (a head that is padded with zeros to d).
     `pieces` [S, T, width] float32: the projection as a split-K product left it; the kernel sums them
     (bfloat16, full rotary, d % 16 == 0 only) and qkv is output only (its q columns are written)."""
     T = qkv.shape[0]
@@ -440,16 +529,19 @@ def rope_kv_write(qkv: torch.Tensor, bias: torch.Tensor | None, pos: torch.Tenso
         _ptr(pos), _ptr(req_slot), _ptr(table), table.shape[1], page_size, _ptr(inv_freq), rot, nq, nkv, d,
         _ptr(k_pages) if write_kv else None, _ptr(v_pages) if write_kv else None, int(write_kv), T,
         _ptr(pieces), splits, plane, int(pairing == "interleaved"), _ptr(q_norm), _ptr(k_norm), float(norm_eps),
-        table.shape[0], k_pages.shape[0] if write_kv else 0, fault_words(qkv.device), _stream()), "rope_kv_write")
+        int(norm_dim), table.shape[0], k_pages.shape[0] if write_kv else 0, fault_words(qkv.device), _stream()), "rope_kv_write")
 
 
 def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                    table: torch.Tensor, page_size: int, pos: torch.Tensor, req_slot: torch.Tensor,
                    nq: int, nkv: int, d: int, window: int | None, scale: float, sink: torch.Tensor | None = None,
-                   keep_first: int = 0, gate: torch.Tensor | None = None) -> None:
+                   keep_first: int = 0, gate: torch.Tensor | None = None, chunk: int | None = None,
+                   slopes: torch.Tensor | None = None) -> None:
     """Exact-order paged attention; q rows `q_stride` elements apart, out [T, nq*d].  `sink` (float32 [nq]): one more
     term exp(sink[h]) in every softmax denominator of head h.  `keep_first` (with a window): the keys at positions below
-    it stay visible beside the window.  `gate` (float32 [T, nq]): the row of (t, h) is multiplied by sigmoid(gate[t, h])."""
+    it stay visible beside the window.  `gate` (float32 [T, nq]): the row of (t, h) is multiplied by sigmoid(gate[t, h]).
+    `chunk` (instead of a window): a query reads the keys of its own chunk of that many positions, counted from position 0.
+    `slopes` (float32 [nq]): the score of key j seen from position p loses slopes[h] * (p - j)."""
     T = out.shape[0]
     if out.shape[1] != nq * d or out.dtype != q.dtype or k_pages.dtype != q.dtype:
         raise KernelError("attn_tokenwise: out must be [T, nq*d] and all tensors of one type")
@@ -462,10 +554,14 @@ def attn_tokenwise(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_pages: t
         raise KernelError("attn_tokenwise: gate must be float32 [T, query heads]")
     if keep_first < 0:
         raise KernelError("attn_tokenwise: keep_first must not be negative")
+    if chunk and window:
+        raise KernelError("attn_tokenwise: a window or chunks, not both")
+    _sink(slopes, nq, "attn_tokenwise (slopes)")
     _check(core().tl_attn_tokenwise(_ptr(q), q_stride, _ptr(out), dtype_code(q.dtype), _ptr(k_pages), _ptr(v_pages),
                                     _ptr(table), table.shape[1], page_size, _ptr(pos), _ptr(req_slot), T, nq, nkv, d,
-                                    int(window or 0), float(scale), _ptr(sink), int(keep_first), _ptr(gate), table.shape[0],
-                                    k_pages.shape[0], fault_words(out.device), _stream()), "attn_tokenwise")
+                                    int(window or 0), float(scale), _ptr(sink), int(keep_first), _ptr(gate), int(chunk or 0),
+                                    _ptr(slopes), table.shape[0], k_pages.shape[0], fault_words(out.device), _stream()),
+           "attn_tokenwise")
 
 
 def _sink(sink, nq: int, who: str) -> None:
@@ -645,8 +741,8 @@ def topk_softmax(z: torch.Tensor, top: int, idx: torch.Tensor, wts: torch.Tensor
 
 
 def route_groups(z: torch.Tensor, correction: torch.Tensor | None, top: int, groups: int, keep: int, group_top: int, scale: float,
-                 idx: torch.Tensor, wts: torch.Tensor) -> None:
-    """Per row of z (float32 [T, E]): s = sigmoid(z); the choice scores are s + correction (float32 [E] or None).  The experts
+                 idx: torch.Tensor, wts: torch.Tensor, softmax: bool = False) -> None:
+    """Per row of z (float32 [T, E]): s = sigmoid(z) (`softmax`: the softmax of z over all E entries); the choice scores are s + correction (float32 [E] or None).  The experts
     form `groups` equal groups of neighbours; a group's score is the sum of its `group_top` largest choice scores; only the
     experts of the `keep` best groups can be chosen.  idx int32 [T, top]: the `top` largest choice scores among them (lowest
     index first on a tie); wts float32 [T, top]: the chosen experts' s divided by their sum (+ 1e-20), times `scale`."""
@@ -659,14 +755,14 @@ def route_groups(z: torch.Tensor, correction: torch.Tensor | None, top: int, gro
         raise KernelError(f"route_groups: {E} experts in {groups} groups, {keep} kept, top {top}")
     _ints(idx, "idx"); _contig(wts, "wts")
     _check(core().tl_route_groups(_ptr(z), z.stride(0), _ptr(correction), E, int(top), int(groups), int(keep), int(group_top),
-                                  float(scale), _ptr(idx), _ptr(wts), T, _stream()), "route_groups")
+                                  int(bool(softmax)), float(scale), _ptr(idx), _ptr(wts), T, _stream()), "route_groups")
 
 
 def moe_up(h: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, a: torch.Tensor, act="relu_squared",
            gated: bool = False, in_scale: torch.Tensor | None = None) -> None:
     """a[t * top + j, :] = act(s w_up[idx[t, j]] h[t]); w_up [E, F, K], a [T * top, F] of h's type; s = in_scale[t, j]
     (float32 [T, top]: the weight on the expert's input) or 1.  `gated`: w_up is [E, 2F, K], an expert's gate rows then its up
-    rows, and a = act(s gate) * (s up)."""
+    rows, and a = act(s gate) * (s up).  An entry idx >= E has no matrices (an identity entry): its rows of a are left alone."""
     T, K = h.shape
     top = idx.shape[1]
     F = a.shape[1]
@@ -677,7 +773,7 @@ def moe_up(h: torch.Tensor, w_up: torch.Tensor, idx: torch.Tensor, a: torch.Tens
         raise KernelError("moe_up: in_scale must be float32 [T, top]")
     _contig(h, "h"); _contig(w_up, "w_up"); _ints(idx, "idx"); _contig(a, "a")
     _check(core().tl_moe_up(_ptr(h), dtype_code(h.dtype), _ptr(w_up), dtype_code(w_up.dtype), _ptr(idx), _ptr(a), T * top, K, F,
-                            top, int(gated), code, _ptr(in_scale), limit, alpha, _stream()), "moe_up")
+                            top, int(gated), code, _ptr(in_scale), limit, alpha, w_up.shape[0], _stream()), "moe_up")
 
 
 def _extra(extra, gate, y, who):
@@ -696,18 +792,21 @@ def _extra(extra, gate, y, who):
 
 
 def moe_down(a: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor | None, y: torch.Tensor,
-             extra: torch.Tensor | None = None, extra_gate: torch.Tensor | None = None) -> None:
+             extra: torch.Tensor | None = None, extra_gate: torch.Tensor | None = None, same: torch.Tensor | None = None) -> None:
     """y[t] = sum_j wts[t, j] * w_down[idx[t, j]] a[t * top + j] (+ sigmoid(extra_gate[t]) * extra[t]); w_down [E, N, F];
-    wts None: an unweighted sum."""
+    wts None: an unweighted sum.  `same` ([T, N] of y's type): an entry idx >= E is an identity entry whose product is same[t]."""
     T, top = idx.shape
     E, N, F = w_down.shape
+    if same is not None and (same.shape != y.shape or same.dtype != y.dtype or not same.is_contiguous()):
+        raise KernelError("moe_down: the identity entries' rows must have y's shape and type")
     if a.shape != (T * top, F) or y.shape != (T, N) or y.dtype != a.dtype or \
             (wts is not None and (wts.dtype != torch.float32 or wts.shape != idx.shape or not wts.is_contiguous())):
         raise KernelError("moe_down: a [T top, F], w_down [E, N, F], y [T, N], wts float32 [T, top]")
     _contig(a, "a"); _contig(w_down, "w_down"); _ints(idx, "idx"); _contig(y, "y")
     g_ptr, ldg = _extra(extra, extra_gate, y, "moe_down")
     _check(core().tl_moe_down(_ptr(a), dtype_code(a.dtype), _ptr(w_down), dtype_code(w_down.dtype), _ptr(idx), _ptr(wts), _ptr(y),
-                              T, F, N, top, _ptr(extra), g_ptr, ldg, _stream()), "moe_down")
+                              T, F, N, top, _ptr(extra), g_ptr, ldg, E if same is not None else (1 << 30), _ptr(same), _stream()),
+           "moe_down")
 
 
 def moe_sort(idx: torch.Tensor, E: int):
@@ -834,30 +933,45 @@ def delta_scan(qkv: torch.Tensor, gates: torch.Tensor, A_log: torch.Tensor, dt_b
 
 def latent_prep(down: torch.Tensor, qr: int, rank: int, dr: int, wq: torch.Tensor, wkv: torch.Tensor, eps: float,
                 inv_freq: torch.Tensor, rot: int, pos: torch.Tensor, req_slot: torch.Tensor, table: torch.Tensor, page_size: int,
-                cq: torch.Tensor, k_pages: torch.Tensor, write_kv: bool = True) -> None:
-    """Per token, from down float32 [T, qr + rank + dr]: cq = the first qr columns RMS-normalised times wq; into the token's
-    place in k_pages [pages, 1, page, d]: the next `rank` columns RMS-normalised times wkv, then the last dr columns with their
-    first `rot` rotated by position (pairs (i, i + rot/2)), then zeros up to d."""
+                cq: torch.Tensor | None, k_pages: torch.Tensor, write_kv: bool = True, pairing: str = "half") -> None:
+    """Per token, from down float32 [T, qr + rank + dr (+ more)]: cq = the first qr columns RMS-normalised times wq; into the
+    token's place in k_pages [pages, 1, page, d]: the next `rank` columns RMS-normalised times wkv, then the next dr columns
+    with their first `rot` rotated by position (pairs (i, i + rot/2), or (2i, 2i + 1) with `pairing` "interleaved"), then zeros
+    up to d.  qr 0 (cq and wq None): there is no query latent; columns behind the first qr + rank + dr are not read."""
     T = down.shape[0]
     d = k_pages.shape[-1]
-    if down.dtype != torch.float32 or down.shape != (T, qr + rank + dr) or cq.shape != (T, qr) or cq.dtype != k_pages.dtype:
-        raise KernelError("latent_prep: down float32 [T, qr + rank + dr], cq [T, qr] of the pages' type")
+    if down.dtype != torch.float32 or down.dim() != 2 or down.shape[1] < qr + rank + dr or down.stride(1) != 1:
+        raise KernelError("latent_prep: down float32 [T, qr + rank + dr or more]")
+    if qr == 0:
+        if cq is not None or wq is not None:
+            raise KernelError("latent_prep: without a query latent there is neither cq nor wq")
+    elif cq.shape != (T, qr) or cq.dtype != k_pages.dtype or wq.numel() != qr or wq.dtype != wkv.dtype:
+        raise KernelError("latent_prep: cq [T, qr] of the pages' type, wq [qr] of wkv's type")
     if tuple(k_pages.shape[1:3]) != (1, page_size) or rank + dr > d:
         raise KernelError("latent_prep: k_pages must be [pages, 1, page, d >= rank + dr]")
-    if wq.numel() != qr or wkv.numel() != rank or wq.dtype != wkv.dtype:
-        raise KernelError("latent_prep: the norms' weights must be [qr] and [rank] of one type")
+    if wkv.numel() != rank:
+        raise KernelError("latent_prep: the latent's norm weight must be [rank]")
     if inv_freq.dtype != torch.float32 or inv_freq.numel() != rot // 2:
         raise KernelError("latent_prep: inv_freq must be float32 [rot/2]")
-    _contig(down, "down"); _contig(cq, "cq"); _contig(k_pages, "k_pages"); _contig(wq, "wq"); _contig(wkv, "wkv")
+    _contig(k_pages, "k_pages"); _contig(wkv, "wkv")
+    if qr:
+        _contig(cq, "cq"); _contig(wq, "wq")
     _ints(pos, "pos"); _ints(req_slot, "req_slot"); _ints(table, "table")
-    _check(core().tl_latent_prep(_ptr(down), qr, rank, dr, _ptr(wq), _ptr(wkv), dtype_code(wq.dtype), float(eps), _ptr(inv_freq),
-                                 int(rot), _ptr(pos), _ptr(req_slot), _ptr(table), table.shape[1], page_size, _ptr(cq),
-                                 _ptr(k_pages), dtype_code(cq.dtype), d, int(write_kv), T, table.shape[0], k_pages.shape[0],
+    _check(core().tl_latent_prep(_ptr(down), down.stride(0), qr, rank, dr, _ptr(wq), _ptr(wkv), dtype_code(wkv.dtype), float(eps),
+                                 _ptr(inv_freq), int(rot), _ptr(pos), _ptr(req_slot), _ptr(table), table.shape[1], page_size,
+                                 _ptr(cq), _ptr(k_pages), dtype_code(k_pages.dtype), d, int(write_kv), T,
+                                 int(_pairing(pairing, "latent_prep")), table.shape[0], k_pages.shape[0],
                                  fault_words(down.device), _stream()), "latent_prep")
 
 
+def _pairing(pairing: str, who: str) -> bool:
+    if pairing not in ("half", "interleaved"):
+        raise KernelError(f"{who}: pairing {pairing!r} is neither 'half' nor 'interleaved'")
+    return pairing == "interleaved"
+
+
 def latent_qrot(q: torch.Tensor, dk: int, dr: int, inv_freq: torch.Tensor, rot: int, pos: torch.Tensor, qa: torch.Tensor,
-                rank: int, H: int) -> None:
+                rank: int, H: int, pairing: str = "half") -> None:
     """qa[t, h, rank : rank + dr] = q[t, h, dk : dk + dr] with its first `rot` dimensions rotated by position; the columns of
     qa behind them are set to zero.  q [T, H (dk + dr)], qa [T, H d]."""
     T = q.shape[0]
@@ -866,7 +980,7 @@ def latent_qrot(q: torch.Tensor, dk: int, dr: int, inv_freq: torch.Tensor, rot: 
         raise KernelError("latent_qrot: q [T, H (dk + dr)], qa [T, H d] of one type, d >= rank + dr")
     _contig(q, "q"); _contig(qa, "qa"); _ints(pos, "pos")
     _check(core().tl_latent_qrot(_ptr(q), dk, dr, _ptr(inv_freq), int(rot), _ptr(pos), _ptr(qa), rank, d, H, T, dtype_code(q.dtype),
-                                 _stream()), "latent_qrot")
+                                 int(_pairing(pairing, "latent_qrot")), _stream()), "latent_qrot")
 
 
 def head_matmul(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, H: int, K: int, N: int, x_head_stride: int,

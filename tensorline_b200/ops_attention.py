@@ -345,6 +345,7 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
                                       _stream()), "attn_decode" + ("+combine" if splits > 1 else ""), launches=2 if splits > 1 else 1)
 
 
+TAKES_CHUNKS = False                # chunks and distance slopes: the exact-order kernel only
 TAKES_KEEP_FIRST = True             # the mma.sync prompt kernel and the cp.async decode kernel read kept first keys beside a window
 
 

@@ -25,6 +25,12 @@ its window, at their true positions.  `sink_value`: the sink is this fixed numbe
 (0.0: the denominator holds one more term 1).  `head_gate` (tensor `head_gate`, [query heads, hidden]): head h's output
 is multiplied by sigmoid(W_g x)_h, one number per token and head computed in float32 from the mixer's input, before the
 output projection.
+
+`chunk` (instead of a window): the sequence is cut into chunks of that many positions counted from position 0, and a query
+reads the keys of its own chunk only; the pages of chunks that lie behind are given back.  `distance_slopes` (one number a
+query head): the score of key j seen from position p loses slope * (p - j), in float32 beside the scaled product.
+`qk_norm_weight` False: the q/k norm has no weights (every head is divided by its root mean square and nothing else); the
+norm then also works over a head that is padded, taking its mean over the head's own size.
 """
 from __future__ import annotations
 
@@ -58,7 +64,8 @@ class PagedAttention(Part):
     def __init__(self, rt: Runtime, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool, position: PartSpec, window: int | None = None, scale: float | None = None,
                  qk_norm_eps: float | None = None, v_head_dim: int | None = None, sink: bool = False,
-                 names: dict | None = None, keep_first: int = 0, sink_value: float | None = None, head_gate: bool = False):
+                 names: dict | None = None, keep_first: int = 0, sink_value: float | None = None, head_gate: bool = False,
+                 chunk: int | None = None, distance_slopes=None, qk_norm_weight: bool = True):
         super().__init__(rt)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
@@ -67,8 +74,15 @@ class PagedAttention(Part):
         d = max(self.dk, self.dv)
         if not rt.exact:
             d = -(-d // 16) * 16                          # the bfloat16 attention kernels take multiples of 16
-        if d != self.dk and qk_norm_eps is not None:
-            raise ValueError("a q/k norm over a padded head is not supported")
+        if d != self.dk and qk_norm_eps is not None and qk_norm_weight:
+            raise ValueError("a weighted q/k norm over a padded head is not supported")
+        if chunk is not None and (window is not None or chunk < 1):
+            raise ValueError("chunks are positive and stand instead of a window")
+        if distance_slopes is not None and len(distance_slopes) != num_heads:
+            raise ValueError(f"{len(distance_slopes)} distance slopes for {num_heads} query heads")
+        self.chunk, self.qk_norm_weight = chunk, bool(qk_norm_weight)
+        self.slopes = None if distance_slopes is None else \
+            torch.tensor([float(v) for v in distance_slopes], dtype=torch.float32, device=rt.device)
         self.hidden, self.nq, self.nkv, self.d = hidden, num_heads, num_kv_heads, d
         self.qkv_bias, self.window = qkv_bias, window
         self.keep_first = int(keep_first) if window is not None else 0
@@ -83,7 +97,7 @@ class PagedAttention(Part):
         self.w_qkv = self.b_qkv = self.w_o = self.q_norm = self.k_norm = self.sink = self.w_gate = None
 
     def cache_need(self):
-        return PagedKV(self.nkv, self.d, self.window, keep_first=self.keep_first)
+        return PagedKV(self.nkv, self.d, self.window, keep_first=self.keep_first, chunk=self.chunk)
 
     def expected_tensors(self, prefix):
         H, nq, nkv, dk, dv = self.hidden, self.nq, self.nkv, self.dk, self.dv
@@ -93,7 +107,7 @@ class PagedAttention(Part):
         if self.qkv_bias:
             out.update({n["q_bias"]: TensorSpec((nq * dk,)), n["k_bias"]: TensorSpec((nkv * dk,)),
                         n["v_bias"]: TensorSpec((nkv * dv,))})
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             out.update({n["q_norm"]: TensorSpec((dk,), init="ones"), n["k_norm"]: TensorSpec((dk,), init="ones")})
         if self.has_sink:
             out[n["sink"]] = TensorSpec((nq,))
@@ -114,9 +128,11 @@ class PagedAttention(Part):
         if dv != d:
             w_o = _pad_heads(w_o.t().contiguous(), nq, dv, d).t()
         self.w_o = self._compute_copy(w_o)
-        if self.qk_norm_eps is not None:
+        if self.qk_norm_eps is not None and self.qk_norm_weight:
             self.q_norm = weights[n["q_norm"]].float().contiguous()
             self.k_norm = weights[n["k_norm"]].float().contiguous()
+        elif self.qk_norm_eps is not None:
+            self.q_norm = self.k_norm = torch.ones(d, dtype=torch.float32, device=self.w_o.device)
         if self.has_sink:
             self.sink = weights[n["sink"]].float().contiguous()
         elif self.sink_value is not None:
@@ -147,7 +163,7 @@ class PagedAttention(Part):
         def rotary_kernel():
             ops.rope_kv_write(qkv, self.b_qkv, ctx.pos, ctx.req_slot, table, ctx.page_size, inv_freq, rot,
                               nq, nkv, d, cache.k, cache.v, write_kv=cache.owner, pieces=pieces, pairing=rotary.pairing,
-                              q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.qk_norm_eps or 0.0)
+                              q_norm=self.q_norm, k_norm=self.k_norm, norm_eps=self.qk_norm_eps or 0.0, norm_dim=self.dk)
 
         # A step of single tokens whose attention kernel can do bias, rotation and the page write of its own tokens
         # (the TMA decode kernel) needs no rotary kernel in front of it.

@@ -9,7 +9,7 @@ first norm (or the model's last) as `pending`.
 from __future__ import annotations
 
 from .base import FEED_FORWARDS, MIXERS, NORMS, Part, PartSpec, Runtime, register_block
-from .linear import PairSum, PostNormed, Scaled, resolve
+from .linear import PairSum, PostNormed, Scaled, StreamUpdate, resolve
 
 
 @register_block("pre_norm")
@@ -143,3 +143,50 @@ class SandwichNormBlock(PreNormBlock):
             return a
         h = self.norm2.add_norm(x, a)
         return PostNormed(self.ff.forward(h, ctx), self.post2.weight, self.post2.eps)
+
+
+@register_block("hyper_connections")
+class HyperConnectionBlock(PreNormBlock):
+    """A pre-norm block over `streams` copies x_1 .. x_S of the residual stream (x float32 [T, S * hidden]).  For sublayer
+    q (1: the mixer, 2: the feed-forward) with the layer's tensors `hc<q>.in` [S], `hc<q>.out` [S] and `hc<q>.mix` [S, S]:
+
+        u = sum_s in[s] x_s;   y = sublayer(norm_q(u));   x_r <- sum_s mix[s, r] x_s + out[r] y     for every r at once
+
+    The rebuild of the copies travels as a `StreamUpdate` to the next norm (this block's second, the next block's first or
+    the model's), which applies it, reads the copies with its own `in` and normalises, all in one float32 kernel."""
+
+    def __init__(self, rt: Runtime, mixer: PartSpec, feed_forward: PartSpec | None, norm1: PartSpec, norm2: PartSpec | None,
+                 streams: int, names: dict | None = None):
+        super().__init__(rt, mixer, feed_forward, norm1, norm2, {"hc1": "hc1", "hc2": "hc2", **(names or {})})
+        if not 1 <= streams <= 16:
+            raise ValueError(f"{streams} stream copies: the kernel takes 1 to 16")
+        self.S = int(streams)
+        self.hc = {}
+
+    def _hc_names(self, prefix, q):
+        base = f"{prefix}.{self.names[f'hc{q}']}"
+        return {"in": f"{base}.in", "out": f"{base}.out", "mix": f"{base}.mix"}
+
+    def expected_tensors(self, prefix):
+        from .base import TensorSpec
+        out = super().expected_tensors(prefix)
+        for q in (1, 2) if self.ff is not None else (1,):
+            n = self._hc_names(prefix, q)
+            out[n["in"]] = TensorSpec((self.S,), init="ones")
+            out[n["out"]] = TensorSpec((self.S,), init="ones")
+            out[n["mix"]] = TensorSpec((self.S, self.S))
+        return out
+
+    def bind(self, weights, prefix):
+        super().bind(weights, prefix)
+        for q in (1, 2) if self.ff is not None else (1,):
+            n = self._hc_names(prefix, q)
+            self.hc[q] = {k: weights[n[k]].float().contiguous() for k in ("in", "out", "mix")}      # they enter float32 sums
+
+    def forward(self, x, pending, ctx, cache):
+        h = self.norm1.read_streams(x, pending, self.hc[1]["in"])
+        update = StreamUpdate(self.mixer.forward(h, ctx, cache), self.hc[1]["mix"], self.hc[1]["out"])
+        if self.ff is None:
+            return update
+        h = self.norm2.read_streams(x, update, self.hc[2]["in"])
+        return StreamUpdate(self.ff.forward(h, ctx), self.hc[2]["mix"], self.hc[2]["out"])

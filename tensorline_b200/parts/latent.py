@@ -11,6 +11,11 @@ like ONE key/value head of size rank + dr (padded to what the attention kernels 
 every paged attention kernel of the package serves this mixer unchanged (the value pages are the key pages: a token is
 stored once); the output's first `rank` columns are sum_j p_j c_j, the rest is not read.  The two changes of space are
 products per head (`ops.head_matmul`).  Norm statistics, angles, scores and softmax are float32 in both engines.
+
+Options: `q_rank` None: the queries are one projection of the input (tensor `uq` [H (dk + dr), hidden]), there is no query
+latent; the position encoding may pair (i, i + rot/2) or (2i, 2i + 1); `out_gate`: the heads' outputs, side by side, are
+multiplied element by element by sigmoid(Wg h) (tensor `g` [H dv, hidden], float32 pre-activations: its rows ride in the
+down product) before the output projection.
 """
 from __future__ import annotations
 
@@ -24,19 +29,21 @@ from .linear import matmul, resolve
 # from this many tokens on the bfloat16 engine takes the two products per head to the library (one batched product)
 HEAD_PRODUCT_LIBRARY_MIN_TOKENS = 64
 
-_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o"}
+_NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o",
+          "g": "g"}
 
 
 @register_mixer("latent_attention")
 class LatentAttention(Part):
     graph_capturable = True
 
-    def __init__(self, rt: Runtime, hidden: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int, q_rank: int,
+    def __init__(self, rt: Runtime, hidden: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int, q_rank: int | None,
                  kv_rank: int, scale: float, norm_eps: float, position: PartSpec, window: int | None = None,
-                 names: dict | None = None):
+                 names: dict | None = None, out_gate: bool = False):
         super().__init__(rt)
         self.hidden, self.H, self.dk, self.dr, self.dv = hidden, num_heads, head_dim, rot_dim, v_head_dim
-        self.qr, self.rank, self.scale, self.eps, self.window = q_rank, kv_rank, float(scale), float(norm_eps), window
+        self.qr, self.rank, self.scale, self.eps, self.window = int(q_rank or 0), kv_rank, float(scale), float(norm_eps), window
+        self.out_gate = bool(out_gate)
         d = kv_rank + rot_dim
         self.d = d if rt.exact else -(-d // 16) * 16     # the bfloat16 attention kernels take multiples of 16
         self.position = POSITION_ENCODINGS.build(position, rt, head_dim=rot_dim)
@@ -51,23 +58,28 @@ class LatentAttention(Part):
     def expected_tensors(self, prefix):
         n = {k: f"{prefix}.{v}" for k, v in self.names.items()}
         W, H = self.hidden, self.H
-        return {n["dq"]: TensorSpec((self.qr, W)), n["dq_norm"]: TensorSpec((self.qr,), init="ones"),
-                n["uq"]: TensorSpec((H * (self.dk + self.dr), self.qr)),
-                n["dkv"]: TensorSpec((self.rank + self.dr, W)), n["dkv_norm"]: TensorSpec((self.rank,), init="ones"),
-                n["uk"]: TensorSpec((H * self.dk, self.rank)), n["uv"]: TensorSpec((H * self.dv, self.rank)),
-                n["o"]: TensorSpec((W, H * self.dv))}
+        out = {n["uq"]: TensorSpec((H * (self.dk + self.dr), self.qr or W)),
+               n["dkv"]: TensorSpec((self.rank + self.dr, W)), n["dkv_norm"]: TensorSpec((self.rank,), init="ones"),
+               n["uk"]: TensorSpec((H * self.dk, self.rank)), n["uv"]: TensorSpec((H * self.dv, self.rank)),
+               n["o"]: TensorSpec((W, H * self.dv))}
+        if self.qr:
+            out.update({n["dq"]: TensorSpec((self.qr, W)), n["dq_norm"]: TensorSpec((self.qr,), init="ones")})
+        if self.out_gate:
+            out[n["g"]] = TensorSpec((H * self.dv, W))
+        return out
 
     def bind(self, weights, prefix):
         n = {k: f"{prefix}.{v}" for k, v in self.names.items()}
         H = self.H
         # the down product's float32 accumulators are kept as they are: they feed two norms
-        self.w_down = self._compute_copy(torch.cat([weights[n["dq"]], weights[n["dkv"]]], dim=0))
+        down = ([weights[n["dq"]]] if self.qr else []) + [weights[n["dkv"]]] + ([weights[n["g"]]] if self.out_gate else [])
+        self.w_down = self._compute_copy(torch.cat(down, dim=0))
         self.w_uq = self._compute_copy(weights[n["uq"]])
         self.w_uk = self._compute_copy(weights[n["uk"]].view(H, self.dk, self.rank))                       # [H, K = dk, N = rank]
         self.w_uv = self._compute_copy(weights[n["uv"]].view(H, self.dv, self.rank).transpose(1, 2))       # [H, K = rank, N = dv]
         self.w_o = self._compute_copy(weights[n["o"]])
-        self.n_q = weights[n["dq_norm"]].contiguous()
-        self.n_kv = weights[n["dkv_norm"]].to(self.n_q.dtype).contiguous()
+        self.n_kv = weights[n["dkv_norm"]].contiguous()
+        self.n_q = weights[n["dq_norm"]].to(self.n_kv.dtype).contiguous() if self.qr else None
 
     def forward(self, h, ctx, cache):
         H, d, dk, dr, rank = self.H, self.d, self.dk, self.dr, self.rank
@@ -76,22 +88,23 @@ class LatentAttention(Part):
         rotary = self.position.rotary()
         if not isinstance(rotary, Rotary):
             rotary = Rotary(*rotary)
-        if rotary.pairing != "half":
-            raise NotImplementedError("latent_attention rotates pairs (i, i + rot/2)")
         table = ctx.tables[cache.group]
+        h = resolve(h)
         down = self._down(h)
-        cq = torch.empty((T, self.qr), dtype=act, device=down.device)
+        cq = torch.empty((T, self.qr), dtype=act, device=down.device) if self.qr else None
         ops.latent_prep(down, self.qr, rank, dr, self.n_q, self.n_kv, self.eps, rotary.inv_freq, rotary.rot, ctx.pos, ctx.req_slot,
-                        table, ctx.page_size, cq, cache.k, write_kv=cache.owner)
-        q = resolve(matmul(cq, self.w_uq))
+                        table, ctx.page_size, cq, cache.k, write_kv=cache.owner, pairing=rotary.pairing)
+        q = resolve(matmul(cq if self.qr else h, self.w_uq))
         qa = torch.empty((T, H * d), dtype=act, device=q.device)
         self._per_head(q, self.w_uk, qa, dk, rank, dk + dr, d, ctx)
-        ops.latent_qrot(q, dk, dr, rotary.inv_freq, rotary.rot, ctx.pos, qa, rank, H)
+        ops.latent_qrot(q, dk, dr, rotary.inv_freq, rotary.rot, ctx.pos, qa, rank, H, pairing=rotary.pairing)
         o = torch.empty((T, H * d), dtype=act, device=q.device)
         from . import attention_kernels
         attention_kernels.attend(self, qa, o, ctx, KVCacheView(cache.k, cache.k, cache.group, cache.owner), table)
         ov = torch.empty((T, H * self.dv), dtype=act, device=q.device)
         self._per_head(o, self.w_uv, ov, rank, self.dv, d, self.dv, ctx)
+        if self.out_gate:
+            ops.sigmoid_gate(ov, down[:, self.qr + rank + dr:], ov)
         return matmul(ov, self.w_o)
 
     def _per_head(self, x, w, y, K, N, xs, ys, ctx):
@@ -106,5 +119,5 @@ class LatentAttention(Part):
         ops.mark("library product")
 
     def _down(self, h):
-        """[Wdq; Wdkv] h as float32 [T, qr + rank + dr]."""
+        """[Wdq; Wdkv; Wg] h as float32 [T, qr + rank + dr (+ H dv)]."""
         return resolve(matmul(resolve(h), self.w_down, out_dtype=torch.float32))

@@ -148,6 +148,26 @@ class PairSum:
         self.dtype, self.shape = self.a.dtype, self.a.shape
 
 
+class WeightedPair:
+    """The output of two mixers side by side with fixed weights: alpha a + beta b.  Whoever adds it into the residual stream
+    multiplies and adds in float32 inside its kernel; anyone else calls `resolve`."""
+
+    def __init__(self, a, alpha: float, b, beta: float):
+        self.a, self.b, self.alpha, self.beta = resolve(a), resolve(b), float(alpha), float(beta)
+        self.dtype, self.shape = self.a.dtype, self.a.shape
+
+
+class StreamUpdate:
+    """What a sublayer of a block over several copies of the residual stream leaves behind: its output `value` (a tensor or a
+    `WeightedPair`) with the matrix `mix` [from, to] and the vector `out` that rebuild the copies from it,
+    x_r <- sum_s mix[s, r] x_s + out[r] value.  The next norm does this, its own read of the copies and the norm in one
+    kernel (`RMSNorm.read_streams`)."""
+
+    def __init__(self, value, mix: torch.Tensor, out: torch.Tensor):
+        self.value = value if isinstance(value, WeightedPair) else resolve(value)
+        self.mix, self.out = mix, out
+
+
 def with_row(x: torch.Tensor, pending, row: torch.Tensor, eps: float):
     """`pending` with one more addend: the float32 vector `row`, added once to every row of the stream x."""
     if pending is None:
@@ -170,6 +190,10 @@ def resolve(t):
         return (t.value.float() * t.alpha).to(t.dtype)
     if isinstance(t, PairSum):
         return (t.a.float() + t.b.float()).to(t.dtype)
+    if isinstance(t, WeightedPair):
+        return (t.a.float() * t.alpha + t.b.float() * t.beta).to(t.dtype)
+    if isinstance(t, StreamUpdate):
+        raise TypeError("an update of several stream copies has no value of its own: the next norm applies it")
     if isinstance(t, PendingProduct):
         t = t.run()
     if isinstance(t, NormedInput):

@@ -17,7 +17,9 @@ one number an expert, `correction` True); the experts form `groups` equal groups
 of its `group_score_top` largest choice scores, and only experts of the `keep_groups` best groups can be chosen (the
 others count as minus infinity); the `top` largest choice scores among them are chosen, and their weights are their s
 (without the correction) divided by the sum of the chosen s (+ 1e-20), times `route_scale`.  The activation
-`swish_clamped` comes with `act_limit` and `act_alpha` (see parts/mlp.py).
+`swish_clamped` comes with `act_limit` and `act_alpha` (see parts/mlp.py).  `scoring` "softmax_share" is the same choice
+with s = softmax(z) over all entries of the router.  `identity`: the router has that many entries behind the experts'
+that stand for no matrices: an identity entry's output is the token's input itself (times its weight).
 
 The experts' matrices are stacked ([E, F, K] and [E, K, F]) at load time.  Steps of few tokens stream, for every
 (token, chosen expert) pair, that expert's rows (`ops.moe_up`, `ops.moe_down`): nothing is sorted and nothing comes
@@ -50,23 +52,27 @@ class RoutedExperts(Part):
                  weight_on: str = "output", shared_inner: int | None = None, shared_gate: bool = True,
                  act_limit: float | None = None, act_alpha: float = 1.0, shared_act_limit: float | None = None,
                  correction: bool = False, groups: int = 1, keep_groups: int = 1, group_score_top: int = 2,
-                 route_scale: float = 1.0):
+                 route_scale: float = 1.0, identity: int = 0):
         super().__init__(rt)
         if activation not in ops.GATE_ACTS:
             raise ValueError(f"routed_experts runs one of {sorted(ops.GATE_ACTS)}, not {activation!r}")
-        if scoring not in ("softmax_chosen", "sigmoid", "sigmoid_share") or weight_on not in ("output", "input"):
+        if scoring not in ("softmax_chosen", "sigmoid", "sigmoid_share", "softmax_share") or weight_on not in ("output", "input"):
             raise ValueError(f"routed_experts: scoring {scoring!r} / weight_on {weight_on!r} are not known")
+        if identity < 0 or (identity and (scoring not in ("sigmoid_share", "softmax_share") or weight_on != "output")):
+            raise ValueError("routed_experts: identity entries go with a share scoring and weights on the output")
+        experts_real, experts = experts, experts + identity          # below, `experts` counts the router's entries
         if not 1 <= top <= min(experts, 32) or experts > 1024:
             raise ValueError(f"routed_experts: top {top} of {experts} experts is outside what the choice kernel takes")
         if (activation == "swish_clamped") != (act_limit is not None) or (activation == "swish_clamped" and not gated):
             raise ValueError("routed_experts: 'swish_clamped' is a gated unit and comes with act_limit, and only it")
-        grouped = scoring == "sigmoid_share"
+        grouped = scoring in ("sigmoid_share", "softmax_share")
         if not grouped and (correction or groups != 1 or route_scale != 1.0):
             raise ValueError("routed_experts: a correction, groups and a scale of the weights belong to scoring 'sigmoid_share'")
         if grouped and (groups < 1 or experts % groups or not 1 <= keep_groups <= groups or group_score_top < 1
                         or top > keep_groups * (experts // groups)):
             raise ValueError(f"routed_experts: {experts} experts in {groups} groups, {keep_groups} kept, top {top}")
         self.hidden, self.inner, self.E, self.top, self.router_bias = hidden, inner, experts, top, router_bias
+        self.E_real = experts_real
         self.activation, self.gated, self.scoring, self.weight_on = activation, bool(gated), scoring, weight_on
         self.act = activation if act_limit is None else (activation, float(act_limit), float(act_alpha))
         self.has_correction, self.groups, self.keep_groups = bool(correction), int(groups), int(keep_groups)
@@ -90,7 +96,7 @@ class RoutedExperts(Part):
         out = {f"{prefix}.{self.names['router']}": TensorSpec((self.E, self.hidden))}
         if self.router_bias:
             out[f"{prefix}.{self.names['router_bias']}"] = TensorSpec((self.E,))
-        for e in range(self.E):
+        for e in range(self.E_real):
             if self.gated:
                 out[self._expert(prefix, e, "gate")] = TensorSpec((self.inner, self.hidden))
             out[self._expert(prefix, e, "up")] = TensorSpec((self.inner, self.hidden))
@@ -123,8 +129,8 @@ class RoutedExperts(Part):
             up = weights[self._expert(prefix, e, "up")]
             return torch.cat([weights[self._expert(prefix, e, "gate")], up]) if self.gated else up
 
-        self.w_up = self._compute_copy(torch.stack([stacked(e) for e in range(self.E)]))
-        self.w_down = self._compute_copy(torch.stack([weights[self._expert(prefix, e, "down")] for e in range(self.E)]))
+        self.w_up = self._compute_copy(torch.stack([stacked(e) for e in range(self.E_real)]))
+        self.w_down = self._compute_copy(torch.stack([weights[self._expert(prefix, e, "down")] for e in range(self.E_real)]))
 
     def forward(self, h, ctx):
         h = resolve(h)
@@ -133,9 +139,9 @@ class RoutedExperts(Part):
         ops.small_proj(h, self.w_router, self.b_router, z)
         idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
         wts = torch.empty((T, top), dtype=torch.float32, device=h.device)
-        if self.scoring == "sigmoid_share":
+        if self.scoring in ("sigmoid_share", "softmax_share"):
             ops.route_groups(z[:, :E], self.correction, top, self.groups, self.keep_groups, self.group_score_top, self.route_scale,
-                             idx, wts)
+                             idx, wts, softmax=self.scoring == "softmax_share")
         else:
             ops.topk_softmax(z[:, :E], top, idx, wts, scoring=self.scoring)
         extra = extra_gate = None
@@ -146,7 +152,8 @@ class RoutedExperts(Part):
         if T <= STREAM_MAX_TOKENS or ctx.graph_max_ctx or self.rt.exact:
             a = torch.empty((T * top, self.inner), dtype=h.dtype, device=h.device)
             ops.moe_up(h, self.w_up, idx, a, act=self.act, gated=self.gated, in_scale=wts if on_input else None)
-            ops.moe_down(a, self.w_down, idx, None if on_input else wts, y, extra=extra, extra_gate=extra_gate)
+            ops.moe_down(a, self.w_down, idx, None if on_input else wts, y, extra=extra, extra_gate=extra_gate,
+                         same=h if self.E_real < E else None)
             return y
         offsets, place_of, pair_at = ops.moe_sort(idx, E)
         bounds = offsets.tolist()                        # the one read-back of the step: where every expert's run ends
@@ -154,17 +161,23 @@ class RoutedExperts(Part):
         cap = -(-longest // 64) * 64                     # rows every expert gets in the batched products
         rows = torch.empty((E * cap, self.hidden), dtype=h.dtype, device=h.device)
         ops.moe_gather(h, pair_at, idx, offsets, top, rows, cap=cap, scale=wts.view(-1) if on_input else None)
-        inner = torch.bmm(rows.view(E, cap, self.hidden), self.w_up.transpose(1, 2))             # [E, cap, F] or [E, cap, 2F]
+        R = self.E_real                                  # the entries behind it are identities: their rows pass as they are
+        inner = torch.bmm(rows.view(E, cap, self.hidden)[:R], self.w_up.transpose(1, 2))         # [R, cap, F] or [R, cap, 2F]
         ops.mark("library product")
         if self.gated:
-            act = torch.empty((E * cap, self.inner), dtype=h.dtype, device=h.device)
-            ops.silu_mul(inner.view(E * cap, 2 * self.inner), act, act=self.act)
-            inner = act.view(E, cap, self.inner)
+            act = torch.empty((R * cap, self.inner), dtype=h.dtype, device=h.device)
+            ops.silu_mul(inner.view(R * cap, 2 * self.inner), act, act=self.act)
+            inner = act.view(R, cap, self.inner)
         elif self.activation == "relu_squared":
             ops.relu_square(inner)
         else:
             raise NotImplementedError(f"long steps of experts without a gate run 'relu_squared', not {self.activation!r}")
-        outs = torch.bmm(inner, self.w_down.transpose(1, 2))                                    # [E, cap, K]
+        if R < E:
+            outs = torch.empty((E, cap, self.hidden), dtype=h.dtype, device=h.device)
+            torch.bmm(inner, self.w_down.transpose(1, 2), out=outs[:R])
+            outs[R:].copy_(rows.view(E, cap, self.hidden)[R:])
+        else:
+            outs = torch.bmm(inner, self.w_down.transpose(1, 2))                                # [E, cap, K]
         ops.mark("library product")
         ops.moe_combine(outs.view(E * cap, self.hidden), place_of, idx, offsets, None if on_input else wts, y, cap=cap,
                         extra=extra, extra_gate=extra_gate)

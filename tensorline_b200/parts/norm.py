@@ -5,7 +5,7 @@ import torch
 
 from .. import ops
 from .base import Part, Runtime, TensorSpec, register_norm, tensor_name
-from .linear import FUSE_NORMS, NormedInput, PairSum, PendingProduct, PostNormed, Scaled, SplitSum, resolve
+from .linear import FUSE_NORMS, NormedInput, PairSum, PendingProduct, PostNormed, Scaled, SplitSum, StreamUpdate, WeightedPair, resolve
 
 
 @register_norm("rms_norm")
@@ -54,9 +54,33 @@ class RMSNorm(Part):
         ops.add_rmsnorm_pair(x, a, b, self.weight, None if other is None else other.weight, h, h2, self.eps, rows=rows)
         return h, h2
 
+    def read_streams(self, x, pending, read, rows=None):
+        """x float32 [T, S * dim]: S copies of the residual stream side by side.  `pending` (a `StreamUpdate` or None) is
+        applied to them; then u = sum_r read[r] x_r (`read` float32 [S]; None: the plain sum) is normalised: one kernel,
+        float32 up to the rounding of the result.  With `rows` only those rows are produced and x is left alone."""
+        if self.cast_first or self.one_plus:
+            raise NotImplementedError("several stream copies are read by plain float32 norms")
+        S = x.shape[1] // self.dim
+        n = x.shape[0] if rows is None else rows.numel()
+        h = torch.empty((n, self.dim), dtype=self.rt.act_dtype, device=x.device)
+        kw = {}
+        if pending is not None:
+            v = pending.value
+            if isinstance(v, WeightedPair):
+                kw = {"a": v.a, "alpha": v.alpha, "b": v.b, "beta": v.beta}
+            else:
+                kw = {"a": v}
+            kw.update(mix=pending.mix, out=pending.out)
+        ops.stream_step(x, S, read=read, w=self.weight, eps=self.eps, h=h, rows=rows, **kw)
+        return h
+
     def add_norm(self, x, pending, rows=None, defer=False):
         """`defer`: the caller's next step is a product that takes a `NormedInput`."""
         n = x.shape[0] if rows is None else rows.numel()
+        if isinstance(pending, StreamUpdate) or x.shape[1] != self.dim:       # several copies: their sum is what this norm reads
+            return self.read_streams(x, pending, None, rows=rows)
+        if isinstance(pending, WeightedPair):
+            pending = resolve(pending)
         if isinstance(pending, PairSum):
             if self.cast_first or self.one_plus:
                 x.add_(pending.a.float() + pending.b.float())

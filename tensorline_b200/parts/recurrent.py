@@ -126,10 +126,10 @@ class MLSTM(_MatrixState):
     gate_act = "sigmoid"
 
     def __init__(self, rt: Runtime, hidden: int, num_heads: int, head_dim: int, v_head_dim: int, gate_cap: float,
-                 norm_eps: float, names: dict | None = None):
+                 norm_eps: float, names: dict | None = None, den_eps: float = 1e-6):
         super().__init__(rt, hidden, num_heads, head_dim, v_head_dim, norm_eps, None,
                          {"i": "i", "i_bias": "i.b", "f": "f", "f_bias": "f.b", "norm": "norm", **(names or {})})
-        self.cap = float(gate_cap)
+        self.cap, self.den_eps = float(gate_cap), float(den_eps)
         self.w_gates = self.b_gates = self.head_weight = None
 
     def expected_tensors(self, prefix):
@@ -157,4 +157,4 @@ class MLSTM(_MatrixState):
         gates = torch.empty((h.shape[0], 2 * H), dtype=torch.float32, device=h.device)
         ops.small_proj(h, self.w_gates, self.b_gates, gates)
         ops.linear_scan(proj, 0, H * d, 2 * H * d, H, d, dv, state, ctx.q_start, ctx.slots, ctx.pos, o, B=ctx.B,
-                        gates=gates, cap=self.cap, q_scale=d ** -0.5, den_eps=1e-6, single_tokens=ctx.decode_only)
+                        gates=gates, cap=self.cap, q_scale=d ** -0.5, den_eps=self.den_eps, single_tokens=ctx.decode_only)
