@@ -90,7 +90,15 @@ struct AttnArgs {
     bf16* k_pages_w; bf16* v_pages_w;
     const float* sink;                 // [nq] or null: one more term exp(sink[h]) in every softmax denominator of head h
     int keep_first;                    // with a window: the keys at positions below it stay visible beside the window
+    int seg;                           // > 0 (instead of a window): a query reads the keys of its own segment of `seg` positions
+                                       // only, segments counted from position 0
+    const float* slopes;               // [nq] or null: the score of key j seen from position p loses slopes[h] * (p - j)
 };
+
+// First key a query at position `pos` reads: the start of its segment, of its window, or 0.
+__device__ __forceinline__ int tl_first_key(const AttnArgs& A, int pos) {
+    return A.seg > 0 ? (pos / A.seg) * A.seg : (A.window > 0 ? max(0, pos - A.window + 1) : 0);
+}
 
 // A window with kept first keys reads two runs of keys: [0, keep) and [lo, pos].  The kernels walk tiles of BN keys, so they
 // see the runs as one run of *virtual* positions: the tiles that hold kept keys and lie in front of the window's first tile
@@ -245,19 +253,24 @@ __device__ __forceinline__ float fast_exp2(float x) {          // 2^x, hardware 
 template <int NB, bool MASKED>
 __device__ __forceinline__ void softmax_step(float (&s)[NB][4], float (&o)[D / 8][4], float (&m)[2], float (&l)[2],
                                              const int (&pos_r)[2], const int (&lo_r)[2], int key0, float scale_log2,
-                                             int lane, int keep = 0) {
+                                             int lane, int keep = 0, const float* slope_r = nullptr) {
+    // slope_r (two numbers, in units of log2 e; null: none): row r's score of key j loses slope_r[r] * (pos_r[r] - j).  The
+    // scores are then scaled here, before the maximum is taken, and the exponentials below take them as they are.
     float mx[2] = {-INFINITY, -INFINITY};
+    const bool biased = slope_r != nullptr;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
+            const int j = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+            if (biased) s[nb][e] = fmaf(s[nb][e], scale_log2, -slope_r[r] * (float)(pos_r[r] - j));
             if (MASKED) {
-                const int j = key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
                 if (!(j <= pos_r[r] && (j >= lo_r[r] || j < keep))) s[nb][e] = -INFINITY;
             }
             mx[r] = fmaxf(mx[r], s[nb][e]);
         }
+    if (biased) scale_log2 = 1.0f;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
@@ -321,7 +334,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     const int pos_hi = sp + (row_end - 1) / g;
     tl_checked(pos_hi / A.page_size, A.max_pages, A.lim, TL_K_PREFILL);     // the last table entry this tile reads
     const int pos_first = sp + row0 / g;
-    const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
+    const int key_lo = tl_first_key(A, pos_first);
     const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN;
     // the tiles this block walks: those that hold kept first keys in front of the window's first tile, then kt_lo .. kt_hi
     const int keep = A.window > 0 ? A.keep_first : 0;
@@ -348,17 +361,20 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
     cp_async_commit();
 
     int pos_r[2], lo_r[2];
+    float slope_r[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int R = row0 + warp * 16 + (lane >> 2) + r * 8;
         pos_r[r] = R < rows_total ? sp + R / g : -1;       // -1: no key is visible, the row stays empty
-        lo_r[r] = A.window > 0 ? max(0, pos_r[r] - A.window + 1) : 0;
+        lo_r[r] = pos_r[r] >= 0 ? tl_first_key(A, pos_r[r]) : 0;
+        slope_r[r] = (A.slopes && R < rows_total) ? A.slopes[kh * g + R % g] * LOG2E : 0.f;
     }
+    const float* slope_p = A.slopes ? slope_r : nullptr;
     // the warp's own rows: first and last valid one (positions rise with the row index)
     const int wr_first = row0 + warp * 16, wr_last = min(wr_first + 15, rows_total - 1);
     const bool w_valid = wr_first < rows_total;
     const int w_pos_hi = sp + wr_last / g;
-    const int w_lo = A.window > 0 ? max(0, sp + wr_first / g - A.window + 1) : 0;
+    const int w_lo = tl_first_key(A, sp + wr_first / g);
     float o[D / 8][4];
 #pragma unroll
     for (int nb = 0; nb < D / 8; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
@@ -384,9 +400,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const AttnArgs A) {
         // the tile's keys are all visible to all rows of the warp: below every row's position, inside
         // every row's window
         const bool full = (kt * BN + BN - 1 <= sp + wr_first / g) &&
-                          (A.window <= 0 || kt * BN >= max(0, w_pos_hi - A.window + 1) || kt * BN + BN <= keep);
-        if (full) softmax_step<BN / 8, false>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane);
-        else      softmax_step<BN / 8, true>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane, keep);
+                          (kt * BN >= tl_first_key(A, w_pos_hi) || kt * BN + BN <= keep);
+        if (full) softmax_step<BN / 8, false>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane, 0, slope_p);
+        else      softmax_step<BN / 8, true>(s, o, m, l, pos_r, lo_r, kt * BN, A.scale_log2, lane, keep, slope_p);
         pv_tile<BN / 8>(o, s, sV + buf * BN * DP, 0, lane);
     }
     cp_async_wait<0>();
@@ -428,7 +444,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
     const int split = blockIdx.x / m_tiles, mt = blockIdx.x % m_tiles;
     const int kh = blockIdx.y, b = blockIdx.z;
     const int pos = A.start_pos[b], len = pos + 1;
-    const int lo = A.window > 0 ? max(0, len - A.window) : 0;
+    const int lo = tl_first_key(A, pos);
     const int base = (lo / BN) * BN;
     // the request's keys as a run of virtual positions (see tl_kept_span); a block takes `chunk` of them
     const int keep = A.window > 0 ? A.keep_first : 0;
@@ -483,6 +499,13 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
         ldsm_x4(qf[kb], sQ + ((lane & 7) + ((lane >> 3) & 1) * 8) * DP + kb * 16 + (lane >> 4) * 8);
     const int pos_r[2] = {len - 1, len - 1};               // every row sees the request's keys up to its own
     const int lo_r[2] = {lo, lo};
+    float slope_r[2];                                      // a row is a head of the group
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int hg = mt * 16 + (lane >> 2) + r * 8;
+        slope_r[r] = (A.slopes && hg < g) ? A.slopes[kh * g + hg] * LOG2E : 0.f;
+    }
+    const float* slope_p = A.slopes ? slope_r : nullptr;
     float o[D / 8][4];
 #pragma unroll
     for (int nb = 0; nb < D / 8; ++nb) { o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f; }
@@ -505,8 +528,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnArgs A) {
 #pragma unroll
         for (int nb = 0; nb < 2; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
         qk_tile_regs<2>(s, qf, sK + buf * BN * DP, warp * 16, lane);
-        if (key0 + 16 <= len && (key0 >= lo || key0 + 16 <= keep)) softmax_step<2, false>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane);
-        else softmax_step<2, true>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane, keep);
+        if (key0 + 16 <= len && (key0 >= lo || key0 + 16 <= keep)) softmax_step<2, false>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane, 0, slope_p);
+        else softmax_step<2, true>(s, o, m, l, pos_r, lo_r, key0, A.scale_log2, lane, keep, slope_p);
         pv_tile<2>(o, s, sV + buf * BN * DP, warp * 16, lane);
     }
     cp_async_wait<0>();
@@ -954,7 +977,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 __global__ void attn_combine_kernel(const AttnArgs A) {
     const int head = blockIdx.x, b = blockIdx.y;
     const int len = A.start_pos[b] + 1;
-    const int lo = A.window > 0 ? max(0, len - A.window) : 0;
+    const int lo = tl_first_key(A, len - 1);
     const int base = (lo / BN) * BN;
     const int vlen = tl_kept_span(A.window > 0 ? A.keep_first : 0, base, BN) + len - base;
     const int ns = min(A.splits, (vlen + A.chunk - 1) / A.chunk);
@@ -1050,6 +1073,11 @@ TL_EXPORT int tl_attn_set_sink(const float* sink) { g_sink = sink; return 0; }
 // prompt kernel and the cp.async decode kernel read them; the TMA decode kernel turns such a launch down (code 2).
 static int g_keep_first = 0;
 TL_EXPORT int tl_attn_set_keep_first(int keep_first) { g_keep_first = keep_first > 0 ? keep_first : 0; return 0; }
+// Segments and distance slopes of the launches that follow (see AttnArgs; 0 and null: none).  The mma.sync prompt kernel and
+// the cp.async decode kernel take them; the TMA decode kernel turns such a launch down (code 2).
+static int g_seg = 0;
+static const float* g_slopes = nullptr;
+TL_EXPORT int tl_attn_set_distance(int seg, const float* slopes) { g_seg = seg > 0 ? seg : 0; g_slopes = slopes; return 0; }
 // 1 if this library was compiled as the checking build (-DTL_CHECK=1).
 TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 // Block-table entries a decode block may copy: chunk / page_size of a decode call may not exceed it.
@@ -1073,6 +1101,8 @@ TL_EXPORT int tl_attn_prefill(const void* q, int q_stride, void* out, const void
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
     A.order = order;
     A.keep_first = g_keep_first;
+    A.seg = g_seg; A.slopes = g_slopes;
+    if (g_seg > 0 && window > 0) return 1;
     A.lim = TlLimits{table_rows, total_pages, fault};
     A.q_start = q_start; A.start_pos = start_pos; A.slots = slots;
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
@@ -1103,6 +1133,8 @@ TL_EXPORT int tl_attn_decode(const void* q, int q_stride, void* out, const void*
     A.B = B; A.nq = nq; A.nkv = nkv; A.window = window; A.scale_log2 = scale * LOG2E;
     A.chunk = chunk; A.splits = splits; A.part_o = part_o; A.part_ml = part_ml;
     A.keep_first = g_keep_first;
+    A.seg = g_seg; A.slopes = g_slopes;
+    if (g_seg > 0 && window > 0) return 1;
     A.lim = TlLimits{table_rows, total_pages, fault};
     const int g = nq / nkv, m_tiles = (g + 15) / 16;
     dim3 grid(splits * m_tiles, nkv, B);
@@ -1152,6 +1184,7 @@ int decode_tma_impl(const void* q, int q_stride, void* out, const void* k_pages,
 #if HEAD_DIM % 64 == 0
     if (B <= 0) return 0;
     if (g_keep_first > 0 && window > 0) return 2;          // two runs of keys: the cp.async kernel walks them
+    if (g_seg > 0 || g_slopes != nullptr) return 2;        // segments and distance slopes: the cp.async kernel
     if (R.inv_freq && ((q_stride & 7) || ((uintptr_t)q & 15) || (R.bias && ((uintptr_t)R.bias & 15)))) return 2;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
     // cluster_merge: the key ranges of a (request, KV head) merge inside a thread-block cluster, no partials needed

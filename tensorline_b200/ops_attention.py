@@ -47,6 +47,8 @@ def attn_lib(head_dim: int):
         lib.tl_attn_set_sink.restype = ctypes.c_int
         lib.tl_attn_set_keep_first.argtypes = [_I]
         lib.tl_attn_set_keep_first.restype = ctypes.c_int
+        lib.tl_attn_set_distance.argtypes = [_I, _P]
+        lib.tl_attn_set_distance.restype = ctypes.c_int
         if lib.tl_attn_decode_max_table() != DECODE_MAX_TABLE_ENTRIES:
             raise KernelError(f"the attention library copies {lib.tl_attn_decode_max_table()} block-table entries a block, "
                               f"the split planner assumes {DECODE_MAX_TABLE_ENTRIES}")
@@ -89,6 +91,15 @@ def attn_tc_lib(head_dim: int):
         lib.tl_attn_set_keep_first.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
+
+
+def _set_distance(lib, chunk, slopes, nq: int, window) -> None:
+    """Chunks and distance slopes of the library's launches that follow (None: none).  Set before every launch."""
+    if chunk and window:
+        raise KernelError("attention: a window or chunks, not both")
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != nq or not slopes.is_contiguous() or not slopes.is_cuda):
+        raise KernelError("attention: the distance slopes must be a contiguous float32 device tensor with one entry a query head")
+    lib.tl_attn_set_distance(int(chunk or 0), _ptr(slopes))
 
 
 def _set_sink(lib, sink, nq: int) -> None:
@@ -249,12 +260,15 @@ def plan_splits(batch: int, nkv: int, group: int, span: int, head_dim: int = 128
 
 
 def prefill(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-            nq, nkv, d, window, scale, order=None, sink=None, keep_first: int = 0) -> None:
+            nq, nkv, d, window, scale, order=None, sink=None, keep_first: int = 0, chunk: int | None = None, slopes=None) -> None:
     """Prompt-portion attention on mma.sync tiles of 64 query rows.  `keep_first` (with a window): the keys at positions below
-    it stay visible beside the window; the kernel walks their tiles in front of the window's."""
+    it stay visible beside the window; the kernel walks their tiles in front of the window's.  `chunk` (instead of a
+    window): a query reads the keys of its own chunk of that many positions only; `slopes` (float32 [nq]): the score of key
+    j seen from position p loses slopes[h] * (p - j)."""
     g = nq // nkv
     B = len(h_q_start) - 1
     _set_sink(attn_lib(d), sink, nq)
+    _set_distance(attn_lib(d), chunk, slopes, nq, window)
     attn_lib(d).tl_attn_set_keep_first(int(keep_first) if window else 0)
     tiles = sum(-(-(h_q_start[i + 1] - h_q_start[i]) * g // KEY_TILE) for i in range(B))
     if order is not None:
@@ -285,7 +299,8 @@ def decode_takes_rope(B: int, d: int, page_size: int) -> bool:
 
 def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, B,
            nq, nkv, d, window, scale, chunk, splits, part_o=None, part_ml=None, tma: bool | None = None,
-           cluster: bool | None = None, rope: dict | None = None, sink=None, keep_first: int = 0) -> None:
+           cluster: bool | None = None, rope: dict | None = None, sink=None, keep_first: int = 0, mask_chunk: int | None = None,
+           slopes=None) -> None:
     """Split-KV decode attention.  `tma`: load K and V by TMA (head sizes that are multiples of 64, pages of
     8..64 tokens); None = wherever that applies.  `cluster` (TMA path, 2..8 key ranges, groups of at most 16
     heads): the ranges of a request merge inside a thread-block cluster, no partials, no second kernel;
@@ -296,12 +311,13 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
     if KEY_TILE % page_size:
         raise KernelError(f"page size {page_size} must divide {KEY_TILE}")
     _set_sink(attn_lib(d), sink, nq)
+    _set_distance(attn_lib(d), mask_chunk, slopes, nq, window)      # `mask_chunk`: the chunks of the mask (`chunk` is a block's key range)
     keep_first = int(keep_first) if window else 0
     attn_lib(d).tl_attn_set_keep_first(keep_first)
     # kept first keys beside a window are two runs of keys: the cp.async kernel walks them (`chunk` and `splits` then count
     # the tiles of both runs, see `kept_span`)
     use_tma = (TMA_DECODE and B >= TMA_DECODE_MIN_BATCH if tma is None else tma) and d % 64 == 0 and 8 <= page_size <= 64 \
-        and not keep_first
+        and not keep_first and not mask_chunk and slopes is None
     if rope is not None and not use_tma:
         raise KernelError("attn_decode: the rotary step folds into the TMA kernel only")
     # up to 8 ranges in a cluster of the portable size; 9 to 16 (this GPU's limit) while the clusters are few enough to be
@@ -345,7 +361,7 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
                                       _stream()), "attn_decode" + ("+combine" if splits > 1 else ""), launches=2 if splits > 1 else 1)
 
 
-TAKES_CHUNKS = False                # chunks and distance slopes: the exact-order kernel only
+TAKES_CHUNKS = True                 # the mma.sync prompt kernel and the cp.async decode kernel take chunks and distance slopes
 TAKES_KEEP_FIRST = True             # the mma.sync prompt kernel and the cp.async decode kernel read kept first keys beside a window
 
 
@@ -355,7 +371,7 @@ def kept_span(keep_first: int) -> int:
 
 
 def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale, rope: dict | None = None, sink=None,
-                keep_first: int = 0) -> None:
+                keep_first: int = 0, chunk: int | None = None, slopes=None) -> None:
     """`rope`: only for decode-only steps that `decode_takes_rope` accepted (see `decode`).  `sink`: float32 [nq], one more
     term exp(sink[h]) in the softmax denominators of head h (every kernel adds it once, where a row is finished)."""
     if qkv.dtype != torch.bfloat16 or k_pages.dtype != torch.bfloat16:
@@ -368,21 +384,29 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
         span = ctx.graph_max_ctx or ctx.max_ctx
         if window:
             span = min(span, window + KEY_TILE - 1 + kept_span(keep_first))
+        if chunk:
+            span = min(span, chunk + KEY_TILE - 1)
+        dist = {"mask_chunk": chunk, "slopes": slopes}
         chunk, splits = plan_splits(ctx.B, nkv, nq // nkv, span, d, page_size=ctx.page_size)
         part_o = part_ml = None
         if splits > 1:
             part_o = torch.empty((ctx.B, nq, splits, d), dtype=torch.float32, device=qkv.device)
             part_ml = torch.empty((ctx.B, nq, splits, 2), dtype=torch.float32, device=qkv.device)
         decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
-               ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, rope=rope, sink=sink, keep_first=keep_first)
+               ctx.B, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, rope=rope, sink=sink, keep_first=keep_first,
+               **dist)
     else:
         g = nq // nkv
+        dist = {"mask_chunk": chunk, "slopes": slopes}
+        mask_chunk = chunk
         singles = _single_token_requests(ctx, qkv.device, g, nkv)
         skip = singles["set"] if singles else frozenset()
         if singles:
             # the single decoded tokens of a mixed step: the decode kernel cuts their keys into ranges, where a
             # query tile of the portion kernels would walk one request's whole context with 1 row in 18 used
             span = min(singles["span"], window + KEY_TILE - 1 + kept_span(keep_first)) if window else singles["span"]
+            if mask_chunk:
+                span = min(span, mask_chunk + KEY_TILE - 1)
             n = len(skip)
             chunk, splits = plan_splits(n, nkv, g, span, d, page_size=ctx.page_size)
             part_o = part_ml = None
@@ -401,13 +425,13 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
                     side.wait_event(ready)
                     decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, singles["rows"], singles["start_pos"],
                            singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, sink=sink,
-                           keep_first=keep_first)
+                           keep_first=keep_first, **dist)
                     joined = torch.cuda.Event()
                     joined.record(side)
             else:
                 decode(qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, singles["rows"], singles["start_pos"],
                        singles["slots"], n, nq, nkv, d, window, scale, chunk, splits, part_o, part_ml, sink=sink,
-                       keep_first=keep_first)
+                       keep_first=keep_first, **dist)
         rest = [i for i in range(ctx.B) if i not in skip]
         rest_rows = sum(ctx.h_q_start[i + 1] - ctx.h_q_start[i] for i in rest) * g
         # Steps whose requests bring enough query rows to fill 128-row tiles run on tcgen05, and so do steps with a
@@ -415,8 +439,9 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
         # 14B head counts: 129 against 169 us); steps of mostly single tokens beside a short portion keep the 64-row
         # mma.sync tiles.
         # (the pair kernel walks one run of keys: a window with kept first keys takes the one-tile kernel)
+        # (chunks and distance slopes: the mma.sync tiles)
         use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and \
-            (rest_rows >= 96 * len(rest) or rest_rows >= 8 * TC_QUERY_TILE)
+            (rest_rows >= 96 * len(rest) or rest_rows >= 8 * TC_QUERY_TILE) and not mask_chunk and slopes is None
         args = (qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                 ctx.h_q_start, nq, nkv, d, window, scale)
         # Two query tiles a block pay as soon as the one-tile kernel's blocks (one an SM) would need a second round:
@@ -457,7 +482,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
         elif use_tc:
             prefill_tc(*args, order(TC_QUERY_TILE), sink=sink, keep_first=keep_first)
         else:
-            prefill(*args, order(KEY_TILE), sink=sink, keep_first=keep_first)
+            prefill(*args, order(KEY_TILE), sink=sink, keep_first=keep_first, chunk=mask_chunk, slopes=slopes)
         if singles and joined is not None:
             torch.cuda.current_stream(qkv.device).wait_event(joined)
 

@@ -28,6 +28,6 @@ def attend(mixer, qkv, o, ctx, cache, table, rope=None, gate=None) -> None:
                            slopes=slopes)
         return
     ops_attention.attend_bf16(qkv, o, ctx, cache.k, cache.v, table, nq, nkv, d, mixer.window, mixer.scale, rope=rope, sink=sink,
-                              keep_first=keep_first)
+                              keep_first=keep_first, chunk=chunk, slopes=slopes)
     if gate is not None:
         ops.head_gate(o, gate, nq, d)

@@ -25,6 +25,7 @@ n(v; w) = v / sqrt(mean(v^2) + eps) * w and u(v) = v / sqrt(mean(v^2) + eps) wit
   experts    p = softmax(Wrouter h) over experts + identity entries; c = p + correction; the `top` largest c are chosen;
              weights p_e / (sum of the chosen p + 1e-20); an entry e >= experts gives h itself; an expert gives
              Wdown (silu(Wgate h) * Wup h);  y = sum_e weight_e out_e + shared unit(h)
+             without `streams` in the configuration there is one stream and X' = X + y
   output     logits = cap tanh(Whead n(sum_s X_s; final.norm) / cap), cap = logit_softcap
 """
 from __future__ import annotations
@@ -189,7 +190,9 @@ def sub(w, prefix):
 
 
 def streams_step(X, hc, norm_w, eps, fn):
-    """One sublayer over the streams X [S, T, W]."""
+    """One sublayer over the streams X [S, T, W]; without hyper-connection tensors (`hc` empty) the one stream takes the sum."""
+    if not hc:
+        return X + fn(normed(X[0], norm_w, eps))[None]
     z = torch.einsum("s,stw->tw", hc["in"], X)
     y = fn(normed(z, norm_w, eps))
     return torch.einsum("sr,stw->rtw", hc["mix"], X) + hc["out"][:, None, None] * y[None]
@@ -210,11 +213,35 @@ def forward(config: dict, weights: dict, tokens, per_layer: bool = False):
         if layer["mlp"] is not None:
             X = streams_step(X, sub(lw, "hc2"), lw["norm2"], eps, lambda h: experts(h, sub(lw, "mlp"), layer["mlp"]))
         sums.append(X.sum(0))
-    cap = float(config["logit_softcap"])
-    logits = cap * torch.tanh((normed(X.sum(0), w["final.norm"], eps) @ w["head"].T) / cap)
+    logits = normed(X.sum(0), w["final.norm"], eps) @ w["head"].T
+    if config.get("logit_softcap") is not None:
+        cap = float(config["logit_softcap"])
+        logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(sums)) if per_layer else logits
 
 
 def load(folder):
     folder = Path(folder)
     return json.loads((folder / "config.json").read_text()), read_safetensors(folder / "model.safetensors")
+
+
+class PlainTenalorn:
+    def __init__(self, folder):
+        self.cfg, self.weights = load(folder)
+
+
+def logits_of(model: PlainTenalorn, tokens, layers: list | None = None):
+    """Logits [T, vocab]; `layers`, if given, receives the sum of the streams after every layer."""
+    out, sums = forward(model.cfg, model.weights, tokens, per_layer=True)
+    if layers is not None:
+        layers.extend(sums)
+    return out
+
+
+def greedy_generate(model: PlainTenalorn, prompt, n: int) -> list:
+    seq, out = list(prompt), []
+    for _ in range(n):
+        tok = int(torch.argmax(logits_of(model, seq)[-1]))
+        out.append(tok)
+        seq.append(tok)
+    return out
