@@ -604,11 +604,32 @@ def _sumuvik_sizes(z):
             "layers": [order[i % 4] for i in range(z["layers"])]}
 
 
+def _tenalorn_sizes(z):
+    """Four layers: three pairs of chunked attention (chunks of 1,024 positions, a slope per head) beside the matrix memory, and
+    attention through a latent as wide as the widest head the tensor-core attention takes; four copies of the residual stream,
+    the table of token pairs, routed experts with a quarter as many identity entries beside a shared expert, capped logits."""
+    moe = {"expert": {"ff": z["ff"]}, "kind": "moe", "router": {"experts": z["experts"], "identity": z["experts"] // 4, "top": z["top"]},
+           "shared": {"ff": z["ff"]}}
+    pair = {"type": "parallel", "mlp": moe, "mixer": {
+        "left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head"], "vdim": z["head"], "scale": z["head"] ** -0.5,
+                 "mask": {"size": 1024}},
+        "left_scale": 1.0, "right_scale": 1.0,
+        "right": {"heads": z["rec_heads"], "dim": z["rec_dim"], "vdim": z["rec_vdim"], "gate_cap": 15.0}}}
+    latent = {"type": "latent_attention", "mlp": moe, "mixer": {
+        "heads": z["heads"], "dim": z["head"], "rot_dim": 64, "rot": {"base": 500000.0, "dims": 64}, "vdim": z["head"],
+        "kv_rank": 192, "scale": (z["head"] + 64) ** -0.5}}
+    order = [pair, pair, latent, pair]
+    return {"architecture": "Tenalorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "streams": 4,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "logit_softcap": 30.0,
+            "layers": [order[i % 4] for i in range(z["layers"])]}
+
+
 def run_design(a):
     import torch
     from tensorline_b200 import Engine, Qwen2Config
     from tensorline_b200.config.dekerax import DekeraxConfig
     from tensorline_b200.config.sumuvik import SumuvikConfig
+    from tensorline_b200.config.tenalorn import TenalornConfig
     from tensorline_b200.config.vutesun import VutesunConfig
     if not torch.cuda.is_available():
         print(json.dumps({"impl": "ours", "error": "no CUDA device: this engine runs on the GPU only"}))
@@ -628,6 +649,8 @@ def run_design(a):
             arms = {"dekerax": DekeraxConfig.from_dict(_dekerax_sizes(z)), "vutesun": arms["vutesun"]}
         if a.design == "sumuvik":                                        # its closest: windows, a recurrence behind a convolution, a shared expert
             arms = {"sumuvik": SumuvikConfig.from_dict(_sumuvik_sizes(z)), "dekerax": DekeraxConfig.from_dict(_dekerax_sizes(z))}
+        if a.design == "tenalorn":                                       # its closest: a pair of mixers, the matrix memory, routed experts
+            arms = {"tenalorn": TenalornConfig.from_dict(_tenalorn_sizes(z)), "vutesun": arms["vutesun"]}
         out[tag] = {"sizes": dict(z, dense_intermediate=dense)}
         for name, cfg in arms.items():
             weights = random_weights(cfg, device)
@@ -651,7 +674,7 @@ def run_design(a):
             import gc
             gc.collect(); torch.cuda.empty_cache()
     first = out[sorted(out)[0]]
-    beside = {"vutesun": "Qwen2", "dekerax": "Vutesun", "sumuvik": "Dekerax"}[a.design]
+    beside = {"vutesun": "Qwen2", "dekerax": "Vutesun", "sumuvik": "Dekerax", "tenalorn": "Vutesun"}[a.design]
     print(json.dumps({"metric": f"decode tok/s of the {a.design.capitalize()} decoder beside {beside} at equal layer sizes (bf16, batch {batch}, context {context})",
                       "value": first[a.design][f"decode_b{batch}_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
                       "ms_per_step": first[a.design][f"decode_b{batch}_ms"], "higher_is_better": True, "scaling": "weak",
@@ -690,9 +713,10 @@ def main(argv=None):
     ap.add_argument("--timeline", action="store_true",
                     help="print the time line of one captured decode step from the kernels' own stamps (needs TENSORLINE_B200_TRACE=1)")
     ap.add_argument("--no-warm-mix", dest="warm_mix", action="store_false", help="mix: time the first pass (graph capture included)")
-    ap.add_argument("--design", choices=["vutesun", "dekerax", "sumuvik"], default=None,
+    ap.add_argument("--design", choices=["vutesun", "dekerax", "sumuvik", "tenalorn"], default=None,
                     help="instead of the default workload: this design beside the closest other one at equal layer sizes "
-                         "(vutesun beside Qwen2, dekerax beside vutesun, sumuvik beside dekerax; prefill, decode, --profile)")
+                         "(vutesun beside Qwen2, dekerax beside vutesun, sumuvik beside dekerax, tenalorn beside vutesun; "
+                         "prefill, decode, --profile)")
     ap.add_argument("--design-size", default="", help="--design: which of the sizes (2k, 4k; commas between them; default all)")
     a = ap.parse_args(argv)
     if a.warmup < 3:

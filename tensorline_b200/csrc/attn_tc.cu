@@ -185,7 +185,17 @@ struct TcAttnArgs {
     // The one-tile kernel only, with a window: the keys at positions below keep_first stay visible to every later row.
     // Their key tiles come first in a block's walk, then the window's.
     int keep_first;
+    // The one-tile kernel only.  seg > 0 (instead of a window): a query reads the keys of its own segment of `seg` positions
+    // only, segments counted from position 0.  slopes ([nq] or null): the score of key j seen from position p loses
+    // slopes[h] * (p - j).
+    int seg;
+    const float* slopes;
 };
+
+// First key a query at position `pos` reads: the start of its segment, of its window, or 0.
+__device__ __forceinline__ int tl_tc_first_key(const TcAttnArgs& A, int pos) {
+    return A.seg > 0 ? (pos / A.seg) * A.seg : (A.window > 0 ? max(0, pos - A.window + 1) : 0);
+}
 
 // One thread's share of a 128-row Q tile, 16-byte chunks r, r + 128, ... of its BM x D / 8 chunks; row = (token, head of
 // the group).  Where 128 is a multiple of the chunks a row has (head sizes 64, 128, 256) a thread keeps its chunk
@@ -275,7 +285,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
     const int* tab = A.table + (size_t)tl_checked(A.slots[b], A.lim.table_rows, A.lim, TL_K_TC_PREFILL) * A.max_pages;
     const int pos_hi = sp + (row_end - 1) / g, pos_first = sp + row0 / g;
     tl_checked(pos_hi / A.page_size, A.max_pages, A.lim, TL_K_TC_PREFILL);  // the last table entry this tile reads
-    const int key_lo = A.window > 0 ? max(0, pos_first - A.window + 1) : 0;
+    const int key_lo = tl_tc_first_key(A, pos_first);
     const int kt_lo = key_lo / BN, kt_hi = pos_hi / BN;
     // step i of the walk reads key tile i while i < n_keep (kept first keys under the window's first tile), then the window's
     const int keep = A.window > 0 ? A.keep_first : 0;
@@ -304,7 +314,11 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
         // ------------------------------------------------------------ softmax and epilogue: thread = row
         const int R = row0 + tid;
         const int pos_r = R < rows_total ? sp + R / g : -1; // -1: no key is visible
-        const int lo_r = A.window > 0 ? max(0, pos_r - A.window + 1) : 0;
+        const int lo_r = pos_r >= 0 ? tl_tc_first_key(A, pos_r) : 0;
+        // with distance slopes the scores are scaled where the slope is taken off, and the exponentials take them as they are
+        const bool biased = A.slopes != nullptr;
+        const float slope_r = (biased && R < rows_total) ? A.slopes[kh * g + R % g] * LOG2E : 0.f;
+        const float sc = biased ? 1.0f : A.scale_log2;
         const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
@@ -326,6 +340,10 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                 tmem_ld32(lane_addr + S_COL + sl * BN + c0, reinterpret_cast<float(&)[32]>(s[c0]));
             tmem_ld_wait();                                 // all parts in flight, one wait
             const int key0 = kt * BN;
+            if (biased) {
+#pragma unroll
+                for (int c = 0; c < BN; ++c) s[c] = fmaf(s[c], A.scale_log2, -slope_r * (float)(pos_r - (key0 + c)));
+            }
             if (!(key0 + BN - 1 <= pos_r && (key0 >= lo_r || key0 + BN <= keep))) {   // not every key of the tile is visible to this row
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
@@ -333,7 +351,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                     if (!(j <= pos_r && (j >= lo_r || j < keep))) s[c] = -INFINITY;
                 }
             }
-            const float mx = row_max(s) * A.scale_log2;
+            const float mx = row_max(s) * sc;
             // Raise the reference maximum only when a tile exceeds it by more than the threshold.  The
             // tensor-memory loads and stores are warp-wide instructions, so the warp corrects O together
             // (factor 1 for rows that do not move) if any of its rows has to.
@@ -370,7 +388,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tc_prefill_kernel(const TcAtt
                 float p[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    p[e] = fast_exp2(fmaf(s[j8 * 8 + e], A.scale_log2, -m_use));
+                    p[e] = fast_exp2(fmaf(s[j8 * 8 + e], sc, -m_use));
                     l4[e & 3] += p[e];
                 }
                 const uint32_t dst = sP + sl * P_BYTES + swz(BM, tid, j8);
@@ -1223,6 +1241,11 @@ TL_EXPORT int tl_attn_set_sink(const float* sink) { g_sink = sink; return 0; }
 // The kept first keys of the one-tile launches that follow (0: none), set before every launch like the sink.
 static int g_keep_first = 0;
 TL_EXPORT int tl_attn_set_keep_first(int keep_first) { g_keep_first = keep_first > 0 ? keep_first : 0; return 0; }
+// Segments and distance slopes of the one-tile launches that follow (see TcAttnArgs; 0 and null: none), set before every launch;
+// the pair kernels turn such a launch down (code 2).
+static int g_seg = 0;
+static const float* g_slopes = nullptr;
+TL_EXPORT int tl_attn_set_distance(int seg, const float* slopes) { g_seg = seg > 0 ? seg : 0; g_slopes = slopes; return 0; }
 // 1 if this library was compiled as the checking build (-DTL_CHECK=1).
 TL_EXPORT int tl_check_build() { return TL_CHECKING; }
 
@@ -1244,6 +1267,8 @@ TL_EXPORT int tl_attn_tc_prefill(const void* q, int q_stride, void* out, const v
     TcAttnArgs A{};
     A.sink = g_sink;
     A.keep_first = window > 0 ? g_keep_first : 0;
+    if (g_seg > 0 && window > 0) return 1;
+    A.seg = g_seg; A.slopes = g_slopes;
     A.q = (const bf16*)q; A.q_stride = q_stride; A.out = (bf16*)out;
     A.k_pages = (const bf16*)k_pages; A.v_pages = (const bf16*)v_pages;
     A.table = table; A.max_pages = max_pages; A.page_size = page_size;
@@ -1295,6 +1320,7 @@ static int tc2_prefill_impl(const void* q, int q_stride, void* out, const void* 
                             const int* merge_rows, int n_merge_rows, cudaStream_t stream) {
 #if HEAD_DIM <= 128
     if (total_tiles <= 0 || B <= 0) return 0;
+    if (g_seg > 0 || g_slopes != nullptr) return 2;        // segments and distance slopes: the one-tile kernel
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
     if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return 2;
     if (nq % nkv || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;
@@ -1386,6 +1412,7 @@ TL_EXPORT int tl_attn_tc3_prefill(const void* q, int q_stride, void* out, const 
                                   int* fault, cudaStream_t stream) {
 #if HEAD_DIM <= 128
     if (total_tiles <= 0 || B <= 0) return 0;
+    if (g_seg > 0 || g_slopes != nullptr) return 2;        // segments and distance slopes: the one-tile kernel
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return 2;
     if (((uintptr_t)k_pages & 127) || ((uintptr_t)v_pages & 127)) return 2;
     if (nq % nkv || (q_stride & 7) || ((uintptr_t)q & 15)) return 1;

@@ -133,6 +133,84 @@ __global__ void __launch_bounds__(256) stream_step_kernel(float* __restrict__ x,
     for (int c = threadIdx.x; c < W; c += blockDim.x) h[(size_t)i * W + c] = from_f<TA>(u[c] * rstd * to_f<TW>(w[c]));
 }
 
+// Four columns a thread (W % 4 == 0, every pointer aligned for it), as many threads as the row has such groups (up to 1,024):
+// a row of up to 4,096 columns is one pass with all of a thread's loads in flight together.
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    return make_float4(__low2float(h[0]), __high2float(h[0]), __low2float(h[1]), __high2float(h[1]));
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(bf16* p, float4 v) {
+    uint2 o;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+    h[0] = __floats2bfloat162_rn(v.x, v.y); h[1] = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+__device__ __forceinline__ float4 fma4(float k, float4 v, float4 acc) {
+    return make_float4(fmaf(k, v.x, acc.x), fmaf(k, v.y, acc.y), fmaf(k, v.z, acc.z), fmaf(k, v.w, acc.w));
+}
+
+// SM: the most copies this instance takes (a thread keeps SM x 4 old values in registers); MAXT: its largest block.
+template <typename TA, typename TW, int SM, int MAXT>
+__global__ void __launch_bounds__(MAXT) stream_step_vec_kernel(float* __restrict__ x, int S, int W, const TA* __restrict__ a, float alpha,
+                                                               const TA* __restrict__ b, float beta, const float* __restrict__ mix,
+                                                               const float* __restrict__ out, const float* __restrict__ read,
+                                                               const TW* __restrict__ w, float eps, TA* __restrict__ h,
+                                                               float* __restrict__ u_out, const int* __restrict__ rows, int write_x) {
+    extern __shared__ __align__(16) float sm[];
+    __shared__ float red[33];
+    float* u = sm;                                         // [W], then mix [S * S], out [S], read [S]
+    float* s_mix = sm + W;
+    float* s_out = s_mix + S * S;
+    float* s_read = s_out + S;
+    const int i = blockIdx.x;
+    for (int k = threadIdx.x; k < S * S; k += blockDim.x) s_mix[k] = mix ? mix[k] : 0.f;
+    for (int k = threadIdx.x; k < S; k += blockDim.x) { s_out[k] = out ? out[k] : 0.f; s_read[k] = read ? read[k] : 1.0f; }
+    grid_dependency_wait();
+    grid_dependency_trigger();
+    __syncthreads();
+    const size_t t = rows ? (size_t)rows[i] : (size_t)i;
+    float* xr = x + t * (size_t)S * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+        float4 old[SM];
+#pragma unroll
+        for (int s = 0; s < SM; ++s) if (s < S) old[s] = ld4(xr + (size_t)s * W + c);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mix) {
+            float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (a) { const float4 av = ld4(a + t * W + c); y = make_float4(alpha * av.x, alpha * av.y, alpha * av.z, alpha * av.w); }
+            if (b) y = fma4(beta, ld4(b + t * W + c), y);
+#pragma unroll
+            for (int r = 0; r < SM; ++r) {
+                if (r < S) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int s = 0; s < SM; ++s) if (s < S) v = fma4(s_mix[s * S + r], old[s], v);
+                    v = fma4(s_out[r], y, v);
+                    if (write_x) st4(xr + (size_t)r * W + c, v);
+                    acc = fma4(s_read[r], v, acc);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < SM; ++r) if (r < S) acc = fma4(s_read[r], old[r], acc);
+        }
+        st4(u + c, acc);
+        ss = fmaf(acc.x, acc.x, ss); ss = fmaf(acc.y, acc.y, ss); ss = fmaf(acc.z, acc.z, ss); ss = fmaf(acc.w, acc.w, ss);
+    }
+    if (u_out) for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) st4(u_out + (size_t)i * W + c, ld4(u + c));
+    if (!h) return;
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)W + eps);
+    for (int c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+        const float4 uv = ld4(u + c), wv = ld4(w + c);
+        st4(h + (size_t)i * W + c, make_float4(uv.x * rstd * wv.x, uv.y * rstd * wv.y, uv.z * rstd * wv.z, uv.w * rstd * wv.w));
+    }
+}
+
 TL_EXPORT int tl_stream_step(float* x, int S, int W, const void* a, float alpha, const void* b, float beta, int act_dtype,
                              const float* mix, const float* out, const float* read, const void* w, int w_dtype, float eps, void* h,
                              float* u_out, const int* rows, int R, int write_x, cudaStream_t stream) {
@@ -141,6 +219,21 @@ TL_EXPORT int tl_stream_step(float* x, int S, int W, const void* a, float alpha,
     const size_t smem = ((size_t)S * S + 2 * S + W) * sizeof(float);
     if (smem > 200 * 1024) return 1;
     if (rows) write_x = 0;
+    const uintptr_t all = (uintptr_t)x | (uintptr_t)a | (uintptr_t)b | (uintptr_t)w | (uintptr_t)h | (uintptr_t)u_out;
+    if (W % 4 == 0 && (all & 15) == 0) {                   // (bfloat16 rows of W % 4 == 0 columns keep the alignment of their base)
+        const int groups = W / 4, most = S <= 4 ? 1024 : S <= 8 ? 512 : 256;
+        const int threads = groups >= most ? most : groups <= 64 ? 64 : ((groups + 31) / 32) * 32;
+#define SV3(TA, TW, SM, MAXT) do { \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(stream_step_vec_kernel<TA, TW, SM, MAXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_after_wait(stream_step_vec_kernel<TA, TW, SM, MAXT>, dim3(R), dim3(threads), smem, stream, x, S, W, (const TA*)a, alpha, (const TA*)b, beta, \
+                          mix, out, read, (const TW*)w, eps, (TA*)h, u_out, rows, write_x); } while (0)
+#define SV(TA, TW) do { if (S <= 4) SV3(TA, TW, 4, 1024); else if (S <= 8) SV3(TA, TW, 8, 512); else SV3(TA, TW, 16, 256); } while (0)
+        if (act_dtype == TL_F32) { if (w_dtype == TL_F32) SV(float, float); else SV(float, bf16); }
+        else { if (w_dtype == TL_F32) SV(bf16, float); else SV(bf16, bf16); }
+#undef SV
+#undef SV3
+        return tl_launch_status();
+    }
 #define SS(TA, TW) do { \
         if (smem > 48 * 1024) cudaFuncSetAttribute(stream_step_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         launch_after_wait(stream_step_kernel<TA, TW>, dim3(R), dim3(256), smem, stream, x, S, W, (const TA*)a, alpha, (const TA*)b, beta, \

@@ -89,6 +89,8 @@ def attn_tc_lib(head_dim: int):
         lib.tl_attn_set_sink.restype = ctypes.c_int
         lib.tl_attn_set_keep_first.argtypes = [_I]
         lib.tl_attn_set_keep_first.restype = ctypes.c_int
+        lib.tl_attn_set_distance.argtypes = [_I, _P]
+        lib.tl_attn_set_distance.restype = ctypes.c_int
         _tc_libs[head_dim] = lib
     return lib
 
@@ -116,9 +118,10 @@ def tc_min_page(head_dim: int) -> int:
 
 
 def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_pos, slots, h_q_start,
-               nq, nkv, d, window, scale, order=None, sink=None, keep_first: int = 0) -> None:
+               nq, nkv, d, window, scale, order=None, sink=None, keep_first: int = 0, chunk: int | None = None, slopes=None) -> None:
     """Prompt-portion attention on tcgen05: 128 query rows per block, S and O in tensor memory.  `keep_first` (with a
-    window): the keys at positions below it stay visible to every later row; a block walks their key tiles first."""
+    window): the keys at positions below it stay visible to every later row; a block walks their key tiles first.
+    `chunk` (instead of a window) and `slopes`: as `prefill` takes them."""
     from .ops_gemm import status_word
     if page_size < tc_min_page(d) or page_size > KEY_TILE or page_size & (page_size - 1):
         raise KernelError(f"page size {page_size}: the tcgen05 attention kernel for head size {d} takes powers of two "
@@ -129,6 +132,7 @@ def prefill_tc(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, st
     if order is not None:
         tiles = order.numel()                           # the array may leave requests out
     _set_sink(attn_tc_lib(d), sink, nq)
+    _set_distance(attn_tc_lib(d), chunk, slopes, nq, window)
     attn_tc_lib(d).tl_attn_set_keep_first(int(keep_first) if window else 0)
     _check(attn_tc_lib(d).tl_attn_tc_prefill(_ptr(q), q_stride, _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(table),
                                              table.shape[1], page_size, _ptr(q_start), _ptr(start_pos), _ptr(slots), B,
@@ -196,6 +200,7 @@ def prefill_tc_pair(q, q_stride, out, k_pages, v_pages, table, page_size, q_star
         tiles = order.numel()
     lib = attn_tc_lib(d)
     _set_sink(lib, sink, nq)
+    _set_distance(lib, None, None, nq, window)             # the pair kernels take neither chunks nor slopes
     if ksplit > 1 and p_in_tmem is not True:
         T = out.shape[0]
         if merge_rows is None:
@@ -361,7 +366,7 @@ def decode(q, q_stride, out, k_pages, v_pages, table, page_size, q_start, start_
                                       _stream()), "attn_decode" + ("+combine" if splits > 1 else ""), launches=2 if splits > 1 else 1)
 
 
-TAKES_CHUNKS = True                 # the mma.sync prompt kernel and the cp.async decode kernel take chunks and distance slopes
+TAKES_CHUNKS = True                 # the one-tile tcgen05 and mma.sync prompt kernels and the cp.async decode kernel take chunks and distance slopes
 TAKES_KEEP_FIRST = True             # the mma.sync prompt kernel and the cp.async decode kernel read kept first keys beside a window
 
 
@@ -439,9 +444,9 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
         # 14B head counts: 129 against 169 us); steps of mostly single tokens beside a short portion keep the 64-row
         # mma.sync tiles.
         # (the pair kernel walks one run of keys: a window with kept first keys takes the one-tile kernel)
-        # (chunks and distance slopes: the mma.sync tiles)
         use_tc = TC_PREFILL and d % 64 == 0 and d <= 256 and ctx.page_size >= tc_min_page(d) and \
-            (rest_rows >= 96 * len(rest) or rest_rows >= 8 * TC_QUERY_TILE) and not mask_chunk and slopes is None
+            (rest_rows >= 96 * len(rest) or rest_rows >= 8 * TC_QUERY_TILE)
+        distant = bool(mask_chunk) or slopes is not None     # chunks and distance slopes: the one-tile kernel or the mma.sync tiles
         args = (qkv, q_stride, o, k_pages, v_pages, table, ctx.page_size, ctx.q_start, ctx.start_pos, ctx.slots,
                 ctx.h_q_start, nq, nkv, d, window, scale)
         # Two query tiles a block pay as soon as the one-tile kernel's blocks (one an SM) would need a second round:
@@ -463,7 +468,7 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
         # 3,584 cached: 54 against 71 us for the one-tile kernel and 77 for the pair kernel alone; 256 tokens: 35
         # against 66; 128 tokens on 8,000 cached: 42 against 127), as long as a run keeps twelve key tiles or more.
         ksplit = 1
-        if use_tc and TC_PAIR and KEY_SPLIT and d <= 128 and not window:
+        if use_tc and TC_PAIR and KEY_SPLIT and d <= 128 and not window and not distant:
             pair_blocks = sum(-(-(ctx.h_q_start[i + 1] - ctx.h_q_start[i]) * g // (2 * TC_QUERY_TILE)) for i in rest) * nkv
             key_tiles = max(-(-(ctx.h_start_pos[i] + ctx.h_q_start[i + 1] - ctx.h_q_start[i]) // KEY_TILE) for i in rest) if rest else 0
             ksplit = min(8, ops.num_sms() // max(1, pair_blocks), key_tiles // 12)
@@ -476,11 +481,11 @@ def attend_bf16(qkv, o, ctx, k_pages, v_pages, table, nq, nkv, d, window, scale,
                 ksplit = 1
         if ksplit >= 2:
             pass
-        elif use_tc and TC_PAIR and not keep_first and one_tile_blocks > ops.num_sms() and \
+        elif use_tc and TC_PAIR and not keep_first and not distant and one_tile_blocks > ops.num_sms() and \
                 prefill_tc_pair(*args, order(2 * TC_QUERY_TILE), sink=sink):
             pass
         elif use_tc:
-            prefill_tc(*args, order(TC_QUERY_TILE), sink=sink, keep_first=keep_first)
+            prefill_tc(*args, order(TC_QUERY_TILE), sink=sink, keep_first=keep_first, chunk=mask_chunk, slopes=slopes)
         else:
             prefill(*args, order(KEY_TILE), sink=sink, keep_first=keep_first, chunk=mask_chunk, slopes=slopes)
         if singles and joined is not None:

@@ -146,13 +146,15 @@ CHUNK_CASES = [  # nq, nkv, d, page, context lengths before the step, tokens in 
 
 
 @pytest.mark.parametrize("case", CHUNK_CASES, ids=[f"q{c[0]}kv{c[1]}d{c[2]}p{c[3]}c{c[6]}s{int(c[7])}" for c in CHUNK_CASES])
-@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "tensor_core_bf16", "step_bf16"])
+@pytest.mark.parametrize("kernel", ["exact_f32", "exact_bf16", "tensor_core_bf16", "tcgen05_bf16", "step_bf16"])
 def test_attention_over_chunks_with_distance_slopes(case, kernel):
     """Decode and prefill attention over scattered pages, queries seeing their own chunk only and scores losing a slope per
     head times the distance, against the plain formula.  In the first request the first key of the last query's chunk and
     the key just in front of it carry planted scores: the query must see the one and not the other."""
     from tensorline_b200 import ops, ops_attention, ops_gemm
     nq, nkv, d, ps, ctx_lens, step_lens, chunk, sloped = case
+    if kernel == "tcgen05_bf16" and (d % 64 or ps > 64):
+        pytest.skip("the tcgen05 kernel takes head sizes that are multiples of 64")
     adt = torch.float32 if kernel == "exact_f32" else torch.bfloat16
     scale = 1.3 * d ** -0.5
     slopes = torch.tensor([2.0 ** (-6.0 * (h + 1) / nq) for h in range(nq)]) if sloped else None
@@ -214,6 +216,9 @@ def test_attention_over_chunks_with_distance_slopes(case, kernel):
                 assert_close(out.view(T, nq, d), torch.cat(want), f"decode, {splits} ranges", **BF16)
             out.zero_()
         ops_attention.prefill(*args, q_start, nq, nkv, d, None, scale, chunk=chunk, slopes=sl)
+    elif kernel == "tcgen05_bf16":                      # the one-tile kernel
+        ops_attention.prefill_tc(q_all, nq * d, out, kd, vd, table, ps, i32(q_start), i32(ctx_lens), i32(list(range(B))), q_start,
+                                 nq, nkv, d, None, scale, chunk=chunk, slopes=sl)
     else:                                               # the step's own choice of kernels
         qkv = torch.zeros(T, (nq + 2 * nkv) * d, dtype=adt, device="cuda")
         qkv[:, :nq * d] = q_all
