@@ -190,6 +190,11 @@ __global__ void __launch_bounds__(32) route_groups_kernel(const float* __restric
     __syncwarp();
     const int per = E / groups;
     // a group's score: the sum of its gtop largest choice scores (all of them, if it has fewer), taken largest first
+    // (every group kept: nothing to judge, all of them are marked as kept right away)
+    if (keep == groups) {
+        for (int g = lane; g < groups; g += 32) gs[g] = INFINITY;
+        __syncwarp();
+    } else
     for (int g = lane; g < groups; g += 32) {
         const float* cg = c + g * per;
         float sum = 0.f, last = INFINITY; int last_i = -1;
@@ -207,7 +212,7 @@ __global__ void __launch_bounds__(32) route_groups_kernel(const float* __restric
     __syncwarp();
     // the groups that stay: `keep` rounds of an arg-max over the groups' scores (lowest index on a tie); a group that was
     // picked is marked by a score of +inf, which no sum of sigmoids and corrections reaches
-    for (int r = 0; r < keep; ++r) {
+    for (int r = 0; r < (keep == groups ? 0 : keep); ++r) {
         float best = -INFINITY; int bi = 0x7fffffff;
         for (int g = lane; g < groups; g += 32) {
             const float v = gs[g];
