@@ -620,7 +620,7 @@ def _tenalorn_sizes(z):
         "kv_rank": 192, "scale": (z["head"] + 64) ** -0.5}}
     order = [pair, pair, latent, pair]
     return {"architecture": "Tenalorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "streams": 4,
-            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "logit_softcap": 30.0,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 7919, "mul_cur": 104729}}, "logit_softcap": 50.0,
             "layers": [order[i % 4] for i in range(z["layers"])]}
 
 

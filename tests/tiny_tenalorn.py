@@ -87,7 +87,7 @@ N6 = _model(300, 192, 1e-5, 4.0, [
     {"type": "parallel", "mixer": _pair(8, 2, 128, 64, 0.06, 150, 4, 64, 64, 12.0, 1.2, 0.5), "mlp": _moe(48, 12, 4, 4, 64)},
     {"type": "latent_attention", "mixer": _latent(4, 32, 32, 64, 96, 0.15, 10000.0, 32), "mlp": _moe(40, 8, 0, 2)},
     {"type": "parallel", "mixer": _pair(4, 4, 64, 128, 0.1, 96, 2, 128, 64, 10.0, 0.7, 1.0), "mlp": None},
-], streams=4, pairs=(509, 3, 5), cap=30.0)
+], streams=4, pairs=(521, 3, 5), cap=25.0)
 CONFIGS = {"N1": N1, "N2": N2, "N3": N3, "N4": N4, "N5": N5, "N6": N6}
 PAGE_SIZE = {"N1": 8, "N2": 16, "N3": 4, "N4": 16, "N5": 16, "N6": 32}
 
