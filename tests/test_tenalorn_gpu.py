@@ -5,8 +5,13 @@ again; the edges of the chunks in prompts and in decoding; the previous token ac
 CUDA graphs; greedy generation through `Engine.generate` and the scheduler."""
 
 import copy
+import json
+import subprocess
+import sys
+from pathlib import Path
 from types import SimpleNamespace
 
+import numpy as np
 import pytest
 import torch
 
@@ -533,3 +538,33 @@ def test_generate_from_the_command_line(model, capsys):
     import json
     lines = [json.loads(l) for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
     assert [l["token_ids"] for l in lines] == [greedy_generate(model["plain"], [5, 9, 40, 17], 5), greedy_generate(model["plain"], [7], 5)]
+
+
+def test_the_replay_program_with_this_design(model, tmp_path):
+    """`bin/trace_run` itself, bfloat16: JSON lines in, `done <step>` lines and <step>.f32 files out; a request that is left
+    out of a step, one that starts in another's freed slot, portions of two tokens."""
+    if model["name"] != "N1":
+        pytest.skip("one configuration is enough for the command-line protocol")
+    reqs = model["reqs"]
+    a, b, c = reqs["r3"], reqs["r4"], reqs["r2"]
+    lines = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}, {"id": "b", "tokens": b[:2], "want": [1]}], "end": []},
+        {"step": 1, "entries": [{"id": "b", "tokens": b[2:], "want": [len(b) - 3]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": a[30:32], "want": []}, {"id": "c", "tokens": c, "want": [len(c) - 1]}], "end": ["c"]},
+        {"step": 3, "entries": [{"id": "a", "tokens": a[32:], "want": [len(a) - 33]}], "end": ["a"]},
+    ]
+    out = tmp_path / "out"
+    root = Path(__file__).resolve().parent.parent
+    proc = subprocess.run([sys.executable, str(root / "bin" / "trace_run"), "--model", str(model["folder"]), "--dtype", "bfloat16",
+                           "--out", str(out), "--max-tokens", "128", "--page-size", "8", "--max-live", "2"],
+                          input="".join(json.dumps(l) + "\n" for l in lines), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    assert sorted(p.name for p in out.iterdir()) == ["0.f32", "1.f32", "2.f32", "3.f32"]
+    V = model["vocab"]
+    got = {n: torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, V).astype(np.float64)) for n in range(4)}
+    assert [got[n].shape[0] for n in range(4)] == [3, 1, 1, 1]
+    wa, wb, wc = model["want"]["r3"], model["want"]["r4"], model["want"]["r2"]
+    top = float(max(w.abs().max() for w in (wa, wb, wc)))
+    for row, ref in ((got[0][0], wa[0]), (got[0][1], wa[29]), (got[0][2], wb[1]), (got[1][0], wb[-1]), (got[2][0], wc[-1]), (got[3][0], wa[-1])):
+        assert float((row - ref).abs().max()) <= 2 * BF16_REL * top
