@@ -74,6 +74,8 @@ class PagedAttention(Part):
         d = max(self.dk, self.dv)
         if not rt.exact:
             d = -(-d // 16) * 16                          # the bfloat16 attention kernels take multiples of 16
+        else:
+            d += d & 1                                    # the kernel that writes the pages works on pairs of dimensions
         if d != self.dk and qk_norm_eps is not None and qk_norm_weight:
             raise ValueError("a weighted q/k norm over a padded head is not supported")
         if chunk is not None and (window is not None or chunk < 1):

@@ -5,7 +5,7 @@ plain pre-norm block); with and without the table of token pairs and the cap on 
 value heads wider and narrower than query heads, head sizes that are no multiples of 16; chunks that are no multiples of
 the page, of one page, of a single position, and no chunks; latents with a rotation over all, part or none of the shared
 key part; routers with none to several identity entries, every entry chosen, with and without a shared expert; layers
-without a feed-forward; pairs only and latent attention only.  The attention scales are large, so that a softmax is
+without a feed-forward; pairs only; odd head sizes.  The attention scales are large, so that a softmax is
 decided by few keys and a key that is wrongly seen (or not seen) shows; the forget gates of the matrix memory lie near
 one, so that a lost or stale state shows many tokens later.
 """
@@ -71,10 +71,10 @@ N3 = _model(77, 40, 1e-5, 2.0, [
     {"type": "parallel", "mixer": _pair(5, 5, 8, 8, 1.1, None, 2, 8, 12, 10.0, 1.0, 0.7), "mlp": _moe(24, 3, 1, 2, 16)},
     {"type": "latent_attention", "mixer": _latent(4, 12, 0, 20, 16, 0.5), "mlp": None},
 ])
-# one copy of the stream (its tensors exist), chunks of a single position, every router entry chosen, latent attention only
+# one copy of the stream (its tensors exist), chunks of a single position, odd head sizes, every router entry chosen
 N4 = _model(64, 32, 1e-6, 1.0, [
     {"type": "latent_attention", "mixer": _latent(2, 8, 6, 8, 8, 0.6, 30.0, 6), "mlp": _moe(8, 2, 2, 4)},
-    {"type": "parallel", "mixer": _pair(2, 1, 8, 8, 0.8, 1, 2, 8, 8, 10.0, 1.0, 1.0), "mlp": _moe(8, 3, 0, 3, 8)},
+    {"type": "parallel", "mixer": _pair(2, 1, 7, 9, 0.8, 1, 2, 8, 8, 10.0, 1.0, 1.0), "mlp": _moe(8, 3, 0, 3, 8)},
 ], streams=1, pairs=(5, 2, 3), cap=8.0)
 # sizes that are multiples of nothing much: a width of 52, a vocabulary of 101, odd inner sizes, five copies, pairs only
 N5 = _model(101, 52, 1e-5, 7.0, [
